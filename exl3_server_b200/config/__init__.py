@@ -1,11 +1,12 @@
 """Typed configurations and the architecture registry."""
 from .fields import ConfigError, KeyReader, read_config_json
 from .llama import LlamaConfig
+from .nibelix import NibelixConfig, NibelixLayer
 from .nikodra import NikodraConfig, NikodraLayer
 from .rigitar import RigitarConfig, RigitarLayer
 from .registry import (Architecture, register_architecture, registered_names,
                        resolve_architecture, unregister_architecture)
 
-__all__ = ["ConfigError", "KeyReader", "read_config_json", "LlamaConfig", "RigitarConfig", "RigitarLayer", "NikodraConfig", "NikodraLayer", "Architecture",
+__all__ = ["ConfigError", "KeyReader", "read_config_json", "LlamaConfig", "RigitarConfig", "RigitarLayer", "NikodraConfig", "NikodraLayer", "NibelixConfig", "NibelixLayer", "Architecture",
            "register_architecture", "registered_names", "resolve_architecture",
            "unregister_architecture"]

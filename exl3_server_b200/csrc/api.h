@@ -20,6 +20,8 @@ int exl3_add_rmsnorm(float* h, const void* y, int y_dtype, float y_scale, const 
                      int H, cudaStream_t stream);
 // interleave 0: gu = [gate (I) | up (I)]; 8: eight gate columns, then the eight up columns of the same features.
 int exl3_silu_mul(const void* gu, void* out, int dtype, int T, int I, int interleave, cudaStream_t stream);
+// The same with another activation on the gate: kind 0 silu, 1 gelu (exact), 2 gelu by the tanh formula.
+int exl3_act_mul(const void* gu, void* out, int dtype, int T, int I, int interleave, int kind, cudaStream_t stream);
 // inv_freq: rot / 2 frequencies; inv_freq_lo: what float32 lost of them, or null (see rope_sincos in common.cuh).
 int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, const float* inv_freq_lo, int rot,
                        float pos_scale, const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride,
@@ -78,6 +80,12 @@ int exl3_attn_tokens_ex(const void* q, int64_t q_row_stride, void* out, int dtyp
                         const int* tok_seq, int T, int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page,
                         int window, int chunk, int sink, float scale, int split_keys, int max_splits, float* scratch,
                         size_t scratch_bytes, cudaStream_t stream);
+// The same with the output as float32 [T, heads, value_dim] when out_f32 is set (whatever the cache's type).
+int exl3_attn_tokens_wide(const void* q, int64_t q_row_stride, void* out, int out_f32, int dtype, const void* k_pool,
+                        const void* v_pool, const int* block_table, int bt_stride, const int* tok_pos,
+                        const int* tok_seq, int T, int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page,
+                        int window, int chunk, int sink, float scale, int split_keys, int max_splits, float* scratch,
+                        size_t scratch_bytes, cudaStream_t stream);
 
 // Token embedding plus a row of a second table picked by a hash of (previous token, token):
 //   h[t] = table[id_t] + extra[(prev_t * mul_prev + id_t * mul_cur) mod buckets],  extra[buckets] for position 0.
@@ -121,10 +129,11 @@ int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const void* k, int64
                      int64_t v_ld, int v_dtype, const void* wraw, int64_t w_ld, int w_dtype, const void* w0,
                      const void* u, int wu_dtype, const float* decay, float* state, const int* slot_ids,
                      const int* row_start, float* out, int B, int T, int heads, int dk, int dv, int max_new,
-                     float* scratch, size_t scratch_bytes, cudaStream_t stream);
-// out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w[h, :] (w null: 1) * silu(gate[t, h, :]) (gate null: 1)
+                     int in_act, float* scratch, size_t scratch_bytes, cudaStream_t stream);
+// out[t, h, :] = o[t, h, :] / rms(o[t, h, :]) * w[h, :] (w null: 1) * silu(gate[t, h, :]) (gate null: 1; gate_kind 1:
+// sigmoid instead of silu).  in_act of exl3_linear_scan: 1 applies silu to r, k and v as they are read.
 int exl3_head_norm_gate(const float* o, const void* w, int w_dtype, const void* gate, int gate_dtype, int64_t gate_ld,
-                        float eps, void* out, int out_dtype, int T, int heads, int dv, cudaStream_t stream);
+                        int gate_kind, float eps, void* out, int out_dtype, int T, int heads, int dv, cudaStream_t stream);
 // out[t] = coef * (a[t] / rms(a[t]) * wa + b[t] / rms(b[t]) * wb), float32 out
 int exl3_normed_sum2(const void* a, const void* b, int ab_dtype, const void* wa, const void* wb, int w_dtype, float eps,
                      float coef, float* out, int T, int H, cudaStream_t stream);
@@ -134,6 +143,8 @@ int exl3_norm_add_norm(float* h, const void* y, int y_dtype, const void* w, int 
                        int w2_dtype, float eps2, void* x, int x_dtype, int T, int H, cudaStream_t stream);
 // kind 0: z/2 (1 + erf(z / sqrt 2)); 1: z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2: tanh(z)
 int exl3_activation(const void* z, int z_dtype, void* out, int out_dtype, int64_t n, int kind, cudaStream_t stream);
+// x <- cap * tanh(x / cap) in place
+int exl3_softcap(float* x, int64_t n, float cap, cudaStream_t stream);
 
 // Attention over latent rows on the tensor cores (bfloat16; see attention_latent.cu).  q [T * H, dk] and out
 // [T * H, dv] hold the rows of each sequence's tokens of this step head by head; the pool holds one row of dk
@@ -277,4 +288,41 @@ int exl3_sample_filtered_cap();
 int exl3_sample_penalties(float* logits, int R, int V, const int* const* counts, const float* params,
                           cudaStream_t stream);
 int exl3_sample_count(int* const* counts, const int* ids, int R, int V, cudaStream_t stream);
+
+// A norm without statistics, y = tanh(alpha x) w + b, and the residual step of layers whose sublayers run side by
+// side (see tanh_norm.cu): when a is given, h += m * (sa * a + sb * b) in place (b may be null); then up to two
+// norms of the residual rows (out1, out2 null: skipped).  rows (no a then): only those rows of h are normed, into
+// [n_rows, H].  Vectors and alphas are float32.
+int exl3_tanh_norm_add(float* h, const void* a, int a_dtype, const void* b, int b_dtype, const float* sa, const float* sb,
+                       float m, const int* rows, int n_rows, const float* w1, const float* b1, const float* alpha1,
+                       void* out1, const float* w2, const float* b2, const float* alpha2, void* out2, int out_dtype,
+                       int T, int H, cudaStream_t stream);
+
+// A routed feed-forward (see moe.cu).  exl3_moe_route: wr float32 [E + extra, W]; idx int32 and wt float32 [T, top];
+// gate_out float32 [T] = sigmoid of the extra row.  exl3_moe_plan: order int32 [P], plan int32 [4 + 3 * max tiles].
+// exl3_moe_gemm: out[p] = act(W[e(p)] A[p / a_div]) for the planned pairs, W [n_experts, N, K]; act 0 none, 1 gelu
+// (exact), 2 gelu by the tanh formula, 3 silu.  exl3_moe_combine: the weighted sum, float32 [T, H]; picks from
+// n_experts on stand for the input x itself; shared (any type) is added times gate (null: as it is).
+int exl3_moe_tile_rows();
+int exl3_moe_max_tiles(int P, int n_experts);
+int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const float* wr, const float* corr, int T, int W, int E,
+                   int extra, int groups, int keep, int top, float scale, int score_kind, int* idx, float* wt,
+                   float* gate_out, cudaStream_t stream);
+int exl3_moe_plan(const int* idx, int P, int n_experts, int* order, int* plan, cudaStream_t stream);
+int exl3_moe_gemm(const void* A, int a_dtype, int64_t lda, int a_div, const void* W, int w_dtype, const int* order,
+                  const int* plan, void* out, int out_dtype, int P, int n_experts, int N, int K, int act,
+                  cudaStream_t stream);
+int exl3_moe_combine(const float* y, const int* idx, const float* wt, const void* x, int x_dtype, int64_t ldx,
+                     const void* shared, int shared_dtype, const float* gate, float* out, int T, int H, int top,
+                     int n_experts, cudaStream_t stream);
+
+// Heads of several maps (see diff_attn.cu): rotation, widened queries and the cache write; and the combination of
+// two maps' outputs.
+int exl3_maps_prep(const void* x, int x_dtype, int64_t ld, int q_off, int k_off, int v_off, int T, int nh, int nkv,
+                   int maps, int d, int dv, int row, int v_row, int rot, const float* f_hi, const float* f_lo,
+                   const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride, int page, void* q_out,
+                   int q_dtype, void* k_pool, void* v_pool, int pool_dtype, cudaStream_t stream);
+int exl3_diff_combine(const void* a, int a_dtype, int a_row, const void* gate, int gate_dtype, int64_t gate_ld,
+                      float lambda, float eps, float mult, void* out, int out_dtype, int out_row, int T, int heads,
+                      int dv, cudaStream_t stream);
 }

@@ -68,6 +68,14 @@ __device__ inline float sink_finish(float m, float& l) {
   return cs;
 }
 
+// An output element in the cache's type or, for callers that go on in float32 (maps that are subtracted from one
+// another), as a float.
+template <typename T>
+__device__ inline void att_store(T* out, int out_f32, int64_t i, float v) {
+  if (out_f32) reinterpret_cast<float*>(out)[i] = v;
+  else Elem<T>::store(out + i, v);
+}
+
 // merge (mo, lo, ao) into (m, l, a)
 template <typename T, int N>
 __device__ inline void merge_state(float& m, float& l, float (&a)[N], float mo, float lo, const float (&ao)[N]) {
@@ -88,7 +96,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
                    const int* __restrict__ tok_seq, int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page,
                    int window, int chunk, int sink, float scale, int split_keys, int max_splits,
-                   float* __restrict__ scratch, int* __restrict__ counters, int lpk) {
+                   float* __restrict__ scratch, int* __restrict__ counters, int lpk, int out_f32) {
   constexpr int VEC = Elem<T>::vec;
   constexpr int NA = R * VEC;
   constexpr int U = R == 1 ? 4 : (R == 2 ? 2 : 1);  // key groups whose loads are issued together
@@ -256,7 +264,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
       const int head = g * G + h0 + hh;
       if (max_splits <= 1) {
         if (sink) aa *= sink_finish<T>(mm, ll);
-        Elem<T>::store(out + ((int64_t)t * nh + head) * hdv + d, aa / ll);
+        att_store<T>(out, out_f32, ((int64_t)t * nh + head) * hdv + d, aa / ll);
       } else {
         float* sc = scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
         sc[d] = aa;
@@ -297,7 +305,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
       float aa = 0.0f;
 #pragma unroll 4
       for (int s2 = 0; s2 < max_splits; ++s2) aa += __ldcg(base + (int64_t)s2 * rec + d) * sw[s2];
-      Elem<T>::store(out + ((int64_t)t * nh + head) * hdv + d, aa * fin / ll);
+      att_store<T>(out, out_f32, ((int64_t)t * nh + head) * hdv + d, aa * fin / ll);
     }
   }
   if (threadIdx.x == 0) counters[(int64_t)t * nkv + g] = 0;
@@ -308,7 +316,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
 // both sums in chunk order.  The records are read with independent loads.
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ scratch, T* __restrict__ out, int nh, int hd,
-                                    int max_splits, int sink) {
+                                    int max_splits, int sink, int out_f32) {
   extern __shared__ float sw[];                      // [max_splits] weights, then [max_splits] sums
   pdl_wait();
   pdl_trigger();
@@ -333,7 +341,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ scratch, T* __rest
     float aa = 0.0f;
 #pragma unroll 4
     for (int s = 0; s < max_splits; ++s) aa += __ldcg(base + (int64_t)s * rec + d) * sw[s];
-    Elem<T>::store(out + ((int64_t)t * nh + head) * hd + d, aa * fin / ll);
+    att_store<T>(out, out_f32, ((int64_t)t * nh + head) * hd + d, aa * fin / ll);
   }
 }
 
@@ -342,7 +350,7 @@ static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const v
                          const void* v_pool, const int* block_table, int bt_stride, const int* tok_pos,
                          const int* tok_seq, int T_, int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page,
                          int window, int chunk, int sink, float scale, int split_keys, int max_splits, float* scratch, int lpk,
-                         cudaStream_t stream) {
+                         int out_f32, cudaStream_t stream) {
   const size_t smem = ((size_t)ATT_WARPS * GT * (hdv + 2) + 2 * (size_t)max_splits) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attn_tokens_kernel<T, GT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -361,12 +369,12 @@ static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const v
   launch_pdl(attn_tokens_kernel<T, GT, R>, grid, dim3(ATT_WARPS * 32), smem, stream,
              static_cast<const T*>(q), q_row_stride, static_cast<T*>(out), static_cast<const T*>(k_pool),
              static_cast<const T*>(v_pool), block_table, bt_stride, tok_pos, tok_seq, nh, nkv, hd, hdv, kv_row, v_row, page,
-             window, chunk, sink, scale, split_keys, max_splits, scratch, counters, lpk);
+             window, chunk, sink, scale, split_keys, max_splits, scratch, counters, lpk, out_f32);
   int rc = launch_status("attn_tokens");
   if (rc) return rc;
   if (max_splits > 1 && !fused_merge) {
     launch_pdl(attn_combine_kernel<T>, dim3(T_, nh), dim3(64), (size_t)2 * max_splits * sizeof(float), stream,
-               (const float*)scratch, static_cast<T*>(out), nh, hdv, max_splits, sink);
+               (const float*)scratch, static_cast<T*>(out), nh, hdv, max_splits, sink, out_f32);
     rc = launch_status("attn_combine");
   }
   return rc;
@@ -376,7 +384,7 @@ template <typename T>
 static int dispatch(const void* q, int64_t q_row_stride, void* out, const void* k_pool, const void* v_pool,
                     const int* block_table, int bt_stride, const int* tok_pos, const int* tok_seq, int T_,
                     int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page, int window, int chunk, int sink,
-                    float scale, int split_keys, int max_splits, float* scratch, cudaStream_t stream) {
+                    float scale, int split_keys, int max_splits, float* scratch, int out_f32, cudaStream_t stream) {
   constexpr int VEC = Elem<T>::vec;
   const int vecs = ceil_div(max(hd, hdv), VEC);       // 16-byte pieces of the wider of a key row and a value row
   int lpk = 1;
@@ -386,7 +394,7 @@ static int dispatch(const void* q, int64_t q_row_stride, void* out, const void* 
 #define EXL3_ATT(GT, RR)                                                                                 \
   return launch_tokens<T, GT, RR>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos, \
                                   tok_seq, T_, nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale, \
-                                  split_keys, max_splits, scratch, lpk, stream)
+                                  split_keys, max_splits, scratch, lpk, out_f32, stream)
   if (R == 1) {
     if (G == 1) EXL3_ATT(1, 1);
     if (G == 2) EXL3_ATT(2, 1);
@@ -421,12 +429,12 @@ extern "C" size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_
   return (size_t)ATT_COUNTER_SLOTS * sizeof(int) + (size_t)T * nh * max_splits * (hd + 2) * sizeof(float);
 }
 
-extern "C" int exl3_attn_tokens_ex(const void* q, int64_t q_row_stride, void* out, int dtype,
-                                   const void* k_pool, const void* v_pool, const int* block_table,
-                                   int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
-                                   int hd, int hdv, int kv_row, int v_row, int page, int window, int chunk, int sink,
-                                   float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
-                                   cudaStream_t stream) {
+extern "C" int exl3_attn_tokens_wide(const void* q, int64_t q_row_stride, void* out, int out_f32, int dtype,
+                                     const void* k_pool, const void* v_pool, const int* block_table,
+                                     int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
+                                     int hd, int hdv, int kv_row, int v_row, int page, int window, int chunk, int sink,
+                                     float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
+                                     cudaStream_t stream) {
   if (T == 0) return 0;
   if (T < 0 || nh < 1 || nkv < 1 || nh % nkv != 0 || hd < 8 || hd % 8 != 0 || hdv < 8 || hdv % 8 != 0 ||
       kv_row < hd || kv_row % 8 != 0 || v_row < hdv || v_row % 8 != 0 || page < 1 || window < 0 || chunk < 0 ||
@@ -454,13 +462,24 @@ extern "C" int exl3_attn_tokens_ex(const void* q, int64_t q_row_stride, void* ou
   if (dtype == DT_F32)
     return dispatch<float>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq, T,
                            nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale, split_keys, max_splits,
-                           scratch, stream);
+                           scratch, out_f32, stream);
   if (dtype == DT_BF16)
     return dispatch<__nv_bfloat16>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos,
                                    tok_seq, T, nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale,
-                                   split_keys, max_splits, scratch, stream);
+                                   split_keys, max_splits, scratch, out_f32, stream);
   set_error("attn_tokens: unsupported element type %d", dtype);
   return ERR_UNSUPPORTED;
+}
+
+extern "C" int exl3_attn_tokens_ex(const void* q, int64_t q_row_stride, void* out, int dtype,
+                                   const void* k_pool, const void* v_pool, const int* block_table,
+                                   int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
+                                   int hd, int hdv, int kv_row, int v_row, int page, int window, int chunk, int sink,
+                                   float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
+                                   cudaStream_t stream) {
+  return exl3_attn_tokens_wide(q, q_row_stride, out, 0, dtype, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq, T,
+                               nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale, split_keys, max_splits,
+                               scratch, scratch_bytes, stream);
 }
 
 extern "C" int exl3_attn_tokens_kv(const void* q, int64_t q_row_stride, void* out, int dtype,

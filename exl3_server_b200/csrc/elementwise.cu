@@ -141,8 +141,15 @@ add_rmsnorm_bf16_kernel(float* h, const __nv_bfloat16* y, float y_scale, const W
 // out[t,i] = silu(gate[t,i]) * up[t,i].  interleave 0: gu[t] = [gate (I) | up (I)];
 // interleave 8: gu[t] = eight gate columns, the eight up columns of the same
 // features, and so on (the layout the fused decode projection's weights have).
+// the gate's activation: 0 silu, 1 gelu (exact, by erf), 2 gelu by the tanh formula
+__device__ inline float gate_act(float g, int kind) {
+  if (kind == 1) return 0.5f * g * (1.0f + erff(g * 0.70710678118654752f));
+  if (kind == 2) return 0.5f * g * (1.0f + tanhf(0.79788456080286536f * (g + 0.044715f * g * g * g)));
+  return g / (1.0f + expf(-g));
+}
+
 __global__ void silu_mul_kernel(const void* __restrict__ gu, void* __restrict__ out, int dtype,
-                                int64_t total, int I, int interleave) {
+                                int64_t total, int I, int interleave, int kind) {
   pdl_wait();
   pdl_trigger();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -159,14 +166,14 @@ __global__ void silu_mul_kernel(const void* __restrict__ gu, void* __restrict__ 
   }
   const float g = load_act(gu, dtype, gi);
   const float u = load_act(gu, dtype, ui);
-  store_any(out, dtype, idx, g / (1.0f + expf(-g)) * u);
+  store_any(out, dtype, idx, gate_act(g, kind) * u);
 }
 
 // The same with 16-byte accesses: a thread makes VEC outputs (I % VEC == 0, and
 // an interleave that is a multiple of VEC).
 template <typename T>
 __global__ void __launch_bounds__(256)
-silu_mul_vec_kernel(const T* gu, T* out, int64_t total_vecs, int I, int interleave) {
+silu_mul_vec_kernel(const T* gu, T* out, int64_t total_vecs, int I, int interleave, int kind) {
   constexpr int VEC = Elem<T>::vec;
   pdl_wait();
   pdl_trigger();
@@ -181,7 +188,7 @@ silu_mul_vec_kernel(const T* gu, T* out, int64_t total_vecs, int I, int interlea
   load_vec_cg(gu + go, g);
   load_vec_cg(gu + uo, u);
 #pragma unroll
-  for (int e = 0; e < VEC; ++e) o[e] = g[e] / (1.0f + expf(-g[e])) * u[e];
+  for (int e = 0; e < VEC; ++e) o[e] = gate_act(g[e], kind) * u[e];
   store_vec(out + t * I + i0, o);
 }
 
@@ -357,11 +364,11 @@ extern "C" int exl3_add_rmsnorm(float* h, const void* y, int y_dtype, float y_sc
   return launch_status("add_rmsnorm");
 }
 
-extern "C" int exl3_silu_mul(const void* gu, void* out, int dtype, int T, int I, int interleave,
-                             cudaStream_t stream) {
+extern "C" int exl3_act_mul(const void* gu, void* out, int dtype, int T, int I, int interleave, int kind,
+                            cudaStream_t stream) {
   const int64_t total = (int64_t)T * I;
   if (total == 0) return 0;
-  if (T < 0 || I < 1 || interleave < 0 || (interleave > 0 && I % interleave != 0)) {
+  if (T < 0 || I < 1 || interleave < 0 || (interleave > 0 && I % interleave != 0) || kind < 0 || kind > 2) {
     set_error("silu_mul: bad sizes T=%d I=%d interleave=%d", T, I, interleave);
     return ERR_BAD_ARGUMENT;
   }
@@ -373,14 +380,19 @@ extern "C" int exl3_silu_mul(const void* gu, void* out, int dtype, int T, int I,
     const unsigned vblocks = (unsigned)((vecs + 255) / 256);
     if (dtype == DT_F32)
       launch_pdl(silu_mul_vec_kernel<float>, dim3(vblocks), dim3(256), 0, stream, static_cast<const float*>(gu),
-                 static_cast<float*>(out), vecs, I, interleave);
+                 static_cast<float*>(out), vecs, I, interleave, kind);
     else
       launch_pdl(silu_mul_vec_kernel<__nv_bfloat16>, dim3(vblocks), dim3(256), 0, stream,
-                 static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), vecs, I, interleave);
+                 static_cast<const __nv_bfloat16*>(gu), static_cast<__nv_bfloat16*>(out), vecs, I, interleave, kind);
     return launch_status("silu_mul");
   }
-  launch_pdl(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, gu, out, dtype, total, I, interleave);
+  launch_pdl(silu_mul_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, gu, out, dtype, total, I, interleave, kind);
   return launch_status("silu_mul");
+}
+
+extern "C" int exl3_silu_mul(const void* gu, void* out, int dtype, int T, int I, int interleave,
+                             cudaStream_t stream) {
+  return exl3_act_mul(gu, out, dtype, T, I, interleave, 0, stream);
 }
 
 extern "C" int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, const float* inv_freq_lo, int rot,
@@ -409,4 +421,23 @@ extern "C" int exl3_rope_kv_write(void* qkv, int dtype, const float* inv_freq, c
                tok_seq, block_table, bt_stride, k_pool, v_pool, nh, nkv, hd, page, write_kv);
   }
   return launch_status("rope_kv_write");
+}
+
+namespace exl3 {
+// x <- cap * tanh(x / cap), float32 in place (a soft limit on logits).
+__global__ void __launch_bounds__(256) softcap_kernel(float* x, int64_t n, float cap, float inv_cap) {
+  pdl_wait();
+  pdl_trigger();
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x)
+    x[i] = cap * tanhf(x[i] * inv_cap);
+}
+}  // namespace exl3
+
+extern "C" int exl3_softcap(float* x, int64_t n, float cap, cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (n < 0 || !(cap > 0.0f) || x == nullptr) { set_error("softcap: bad arguments"); return ERR_BAD_ARGUMENT; }
+  int64_t blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  launch_pdl(exl3::softcap_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, x, n, cap, 1.0f / cap);
+  return launch_status("softcap");
 }

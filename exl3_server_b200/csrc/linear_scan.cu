@@ -34,6 +34,8 @@ __device__ inline float ls_load_act(const void* p, int dtype, int64_t i) {
   return dtype == DT_F32 ? __ldcg(static_cast<const float*>(p) + i)
                          : __bfloat162float(__ldcg(static_cast<const __nv_bfloat16*>(p) + i));
 }
+// what the projections' outputs go through before they enter the recurrence: 0 nothing, 1 silu
+__device__ inline float ls_in(float x, int act) { return act == 1 ? x / (1.0f + expf(-x)) : x; }
 __device__ inline void ls_store(void* p, int dtype, int64_t i, float v) {
   if (dtype == DT_F32) static_cast<float*>(p)[i] = v;
   else static_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v);
@@ -130,6 +132,7 @@ struct ScanArgs {
   float* state; const int* slot_ids; const int* row_start;
   float* out; float* ab; float* snap;
   int heads, dk, dv, places;
+  int act;                                       // see ls_in
 };
 
 // Chunk j of batch row b has a place of its own among floor(T / LS_CHUNK) + B + 1 places.
@@ -189,8 +192,8 @@ __global__ void linear_scan_kernel(ScanArgs a, int phase) {
     for (int idx = threadIdx.x; idx < n * dk; idx += blockDim.x) {
       const int tt = idx / dk, i = idx - tt * dk;
       const int64_t t = s0 + tt;
-      sr[idx] = ls_load_act(a.r, a.rk_dtype, t * a.r_ld + (int64_t)hd * dk + i);
-      sk[idx] = ls_load_act(a.k, a.rk_dtype, t * a.k_ld + (int64_t)hd * dk + i);
+      sr[idx] = ls_in(ls_load_act(a.r, a.rk_dtype, t * a.r_ld + (int64_t)hd * dk + i), a.act);
+      sk[idx] = ls_in(ls_load_act(a.k, a.rk_dtype, t * a.k_ld + (int64_t)hd * dk + i), a.act);
       if (MODE == 0) {
         const float z = ls_load_act(a.wraw, a.w_dtype, t * a.w_ld + (int64_t)hd * dk + i) +
                         ls_load(a.w0, a.wu_dtype, (int64_t)hd * dk + i);
@@ -225,7 +228,7 @@ __global__ void linear_scan_kernel(ScanArgs a, int phase) {
     if (col) {
       for (int tt = 0; tt < n; ++tt) {
         const int64_t t = s0 + tt;
-        const float vj = ls_load_act(a.v, a.v_dtype, t * a.v_ld + (int64_t)hd * dv + j);
+        const float vj = ls_in(ls_load_act(a.v, a.v_dtype, t * a.v_ld + (int64_t)hd * dv + j), a.act);
         const float* rr = sr + tt * dk;
         const float* kk = sk + tt * dk;
         float acc = 0.0f;
@@ -351,8 +354,8 @@ __global__ void __launch_bounds__(LS_Q * LS_MAX_DV, DK <= 64 ? 2 : 1) linear_sca
     for (int e = 0; e < PER; ++e) {
       const int idx = threadIdx.x + e * blockDim.x;
       if (idx < n * DK) {
-        if (phase != 1) sr[idx] = pr[e];
-        sk[idx] = pk[e];
+        if (phase != 1) sr[idx] = ls_in(pr[e], a.act);
+        sk[idx] = ls_in(pk[e], a.act);
         if (MODE == 0) sw[idx] = expf(-expf(pw[e] + ls_load(a.w0, a.wu_dtype, (int64_t)hd * DK + idx % DK)));
       }
     }
@@ -360,7 +363,7 @@ __global__ void __launch_bounds__(LS_Q * LS_MAX_DV, DK <= 64 ? 2 : 1) linear_sca
     float vj[LS_STAGE];
 #pragma unroll
     for (int tt = 0; tt < LS_STAGE; ++tt)
-      vj[tt] = (col && tt < n) ? ls_load_act(a.v, a.v_dtype, (int64_t)(s0 + tt) * a.v_ld + (int64_t)hd * dv + j) : 0.0f;
+      vj[tt] = (col && tt < n) ? ls_in(ls_load_act(a.v, a.v_dtype, (int64_t)(s0 + tt) * a.v_ld + (int64_t)hd * dv + j), a.act) : 0.0f;
     __syncthreads();
     if (s0 + LS_STAGE < hi) fetch(s0 + LS_STAGE);
     if (MODE == 0) {
@@ -453,7 +456,7 @@ __global__ void __launch_bounds__(LS_Q * LS_MAX_DV, DK <= 64 ? 2 : 1) linear_sca
 
 __global__ void __launch_bounds__(128)
 head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, const void* gate, int gate_dtype,
-                      int64_t gate_ld, float eps, void* out, int out_dtype, int n_items, int heads, int dv) {
+                      int64_t gate_ld, int gate_kind, float eps, void* out, int out_dtype, int n_items, int heads, int dv) {
   pdl_wait();
   pdl_trigger();
   const int lane = threadIdx.x & 31;
@@ -473,7 +476,7 @@ head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, c
     if (w) x *= ls_load(w, w_dtype, (int64_t)hd * dv + e);
     if (gate) {
       const float g = ls_load_act(gate, gate_dtype, (int64_t)t * gate_ld + (int64_t)hd * dv + e);
-      x *= g / (1.0f + expf(-g));
+      x *= (gate_kind == 1 ? 1.0f : g) / (1.0f + expf(-g));
     }
     ls_store(out, out_dtype, (int64_t)item * dv + e, x);
   }
@@ -482,8 +485,8 @@ head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, c
 // The same with four values a lane (dv a multiple of 4, at most 128 a head: one piece a lane), float32 weight.
 template <typename TG, typename TO>
 __global__ void __launch_bounds__(128)
-head_norm_gate_vec_kernel(const float* o, const float* __restrict__ w, const TG* gate, int64_t gate_ld, float eps,
-                          TO* out, int n_items, int heads, int dv) {
+head_norm_gate_vec_kernel(const float* o, const float* __restrict__ w, const TG* gate, int64_t gate_ld, int gate_kind,
+                          float eps, TO* out, int n_items, int heads, int dv) {
   pdl_wait();
   pdl_trigger();
   const int lane = threadIdx.x & 31;
@@ -507,7 +510,7 @@ head_norm_gate_vec_kernel(const float* o, const float* __restrict__ w, const TG*
     for (int i = 0; i < 4; ++i) {
       float v = x[i] * inv;
       if (w) v *= w[(int64_t)hd * dv + e + i];
-      if (gate) v *= g[i] / (1.0f + __expf(-g[i]));
+      if (gate) v *= (gate_kind == 1 ? 1.0f : g[i]) / (1.0f + (sizeof(TO) == 4 ? expf(-g[i]) : __expf(-g[i])));
       Elem<TO>::store(out + (int64_t)item * dv + e + i, v);
     }
   }
@@ -553,10 +556,10 @@ extern "C" int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const voi
                                 const void* v, int64_t v_ld, int v_dtype, const void* wraw, int64_t w_ld, int w_dtype,
                                 const void* w0, const void* u, int wu_dtype, const float* decay, float* state,
                                 const int* slot_ids, const int* row_start, float* out, int B, int T, int heads, int dk,
-                                int dv, int max_new, float* scratch, size_t scratch_bytes, cudaStream_t stream) {
+                                int dv, int max_new, int in_act, float* scratch, size_t scratch_bytes, cudaStream_t stream) {
   if (B == 0 || T == 0) return 0;
   if (B < 0 || T < 0 || heads < 1 || dk < 1 || dv < 1 || dv > 1024 || B > 65535 || mode < 0 || mode > 1 ||
-      (mode == 0 && (wraw == nullptr || w0 == nullptr || u == nullptr)) || (mode == 1 && decay == nullptr)) {
+      (mode == 0 && (wraw == nullptr || w0 == nullptr || u == nullptr)) || (mode == 1 && decay == nullptr) || in_act < 0 || in_act > 1) {
     set_error("linear_scan: bad arguments mode=%d rows=%d tokens=%d heads=%d dk=%d dv=%d", mode, B, T, heads, dk, dv);
     return ERR_BAD_ARGUMENT;
   }
@@ -597,6 +600,7 @@ extern "C" int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const voi
   a.r = r; a.r_ld = r_ld; a.k = k; a.k_ld = k_ld; a.rk_dtype = rk_dtype; a.v = v; a.v_ld = v_ld; a.v_dtype = v_dtype;
   a.wraw = wraw; a.w_ld = w_ld; a.w_dtype = w_dtype; a.w0 = w0; a.u = u; a.wu_dtype = wu_dtype; a.decay = decay;
   a.state = state; a.slot_ids = slot_ids; a.row_start = row_start; a.out = out; a.ab = scratch;
+  a.act = in_act;
   a.heads = heads; a.dk = dk; a.dv = dv; a.places = T / LS_CHUNK + B + 1;
   a.snap = scratch ? scratch + (size_t)a.places * heads * ((size_t)dk + (size_t)dk * dv) : nullptr;
   const int threads = regs ? LS_Q * dvr : dvr;
@@ -618,10 +622,10 @@ extern "C" int exl3_linear_scan(int mode, const void* r, int64_t r_ld, const voi
 }
 
 extern "C" int exl3_head_norm_gate(const float* o, const void* w, int w_dtype, const void* gate, int gate_dtype,
-                                   int64_t gate_ld, float eps, void* out, int out_dtype, int T, int heads, int dv,
-                                   cudaStream_t stream) {
+                                   int64_t gate_ld, int gate_kind, float eps, void* out, int out_dtype, int T, int heads,
+                                   int dv, cudaStream_t stream) {
   if (T == 0) return 0;
-  if (T < 0 || heads < 1 || dv < 1) { set_error("head_norm_gate: bad sizes"); return ERR_BAD_ARGUMENT; }
+  if (T < 0 || heads < 1 || dv < 1 || gate_kind < 0 || gate_kind > 1) { set_error("head_norm_gate: bad sizes"); return ERR_BAD_ARGUMENT; }
   const int items = T * heads;
   const bool vec = dv % 4 == 0 && dv <= 128 && (w == nullptr || w_dtype == DT_F32) && aligned16(o) &&
                    (gate == nullptr || gate_ld % 4 == 0);
@@ -629,15 +633,15 @@ extern "C" int exl3_head_norm_gate(const float* o, const void* w, int w_dtype, c
   const dim3 grid(ceil_div(items, 4)), threads(128);
   if (vec && gate_dtype == DT_BF16 && out_dtype == DT_BF16)
     launch_pdl(head_norm_gate_vec_kernel<__nv_bfloat16, __nv_bfloat16>, grid, threads, 0, stream, o, wf,
-               static_cast<const __nv_bfloat16*>(gate), gate_ld, eps, static_cast<__nv_bfloat16*>(out), items, heads, dv);
+               static_cast<const __nv_bfloat16*>(gate), gate_ld, gate_kind, eps, static_cast<__nv_bfloat16*>(out), items, heads, dv);
   else if (vec && gate_dtype == DT_F32 && out_dtype == DT_BF16)
     launch_pdl(head_norm_gate_vec_kernel<float, __nv_bfloat16>, grid, threads, 0, stream, o, wf,
-               static_cast<const float*>(gate), gate_ld, eps, static_cast<__nv_bfloat16*>(out), items, heads, dv);
+               static_cast<const float*>(gate), gate_ld, gate_kind, eps, static_cast<__nv_bfloat16*>(out), items, heads, dv);
   else if (vec && gate_dtype == DT_F32 && out_dtype == DT_F32)
     launch_pdl(head_norm_gate_vec_kernel<float, float>, grid, threads, 0, stream, o, wf, static_cast<const float*>(gate),
-               gate_ld, eps, static_cast<float*>(out), items, heads, dv);
+               gate_ld, gate_kind, eps, static_cast<float*>(out), items, heads, dv);
   else
-    launch_pdl(head_norm_gate_kernel, grid, threads, 0, stream, o, w, w_dtype, gate, gate_dtype, gate_ld, eps, out,
-               out_dtype, items, heads, dv);
+    launch_pdl(head_norm_gate_kernel, grid, threads, 0, stream, o, w, w_dtype, gate, gate_dtype, gate_ld, gate_kind, eps,
+               out, out_dtype, items, heads, dv);
   return launch_status("head_norm_gate");
 }

@@ -1,0 +1,387 @@
+// A routed feed-forward (mixture of experts): the router, the plan of a step's (token, expert) pairs, the experts'
+// two projections as grouped matrix products, and the weighted sum.
+//
+//   router   z = Wr x (float32), s = softmax(z) or sigmoid(z) over all router outputs, choice c = s + correction;
+//            the outputs form equal groups of neighbours, a group's score is its largest c, only the outputs of the
+//            `keep` best groups can be chosen; the `top` largest c among those are the token's picks, each with the
+//            weight s * scale (no renormalisation).  One more row of Wr may follow the router's: its sigmoid is a
+//            gate per token (for a shared expert) that the same kernel leaves beside the picks.
+//   plan     the pairs (token, pick) whose pick is an expert with weights, ordered by expert and cut into tiles of
+//            at most MOE_TM rows of one expert; everything stays on the device (no count reaches the host), so the
+//            step can be part of a recorded graph.
+//   experts  mid[p] = act(W_up[e] x[token(p)]),  y[p] = W_down[e] mid[p], a block per (tile, 64 output features);
+//            a row's sum walks K in order with one float32 accumulator, so it does not depend on the row's tile mates.
+//   sum      out[t] = sum_k weight[t, k] * (y[t, k], or x[t] itself when pick k is an identity output: those are the
+//            router outputs from n_experts on, which have no weights) + gate[t] * shared[t].
+#include "api.h"
+#include "common.cuh"
+
+#include <math.h>
+
+namespace exl3 {
+
+constexpr int RT_TOK = 4;        // tokens a block of the router takes (one a warp for the choice)
+constexpr int RT_KC = 512;       // columns of x staged at a time
+constexpr int MOE_TM = 32;       // rows of a tile
+constexpr int MOE_TN = 64;       // output features of a block
+constexpr int MOE_TK = 32;
+
+__device__ inline float moe_ld(const float* p) { return __ldcg(p); }
+__device__ inline float moe_ld(const __nv_bfloat16* p) { return __bfloat162float(__ldcg(p)); }
+__device__ inline void moe_st(float* p, float v) { *p = v; }
+__device__ inline void moe_st(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+
+// (value, index) of the larger; equal values: the lower index
+__device__ inline void arg_better(float& v, int& i, float ov, int oi) {
+  if (ov > v || (ov == v && oi < i)) { v = ov; i = oi; }
+}
+__device__ inline void warp_argmax(float& v, int& i) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, i, o);
+    arg_better(v, i, ov, oi);
+  }
+}
+
+template <typename TX>
+__global__ void __launch_bounds__(RT_TOK * 32)
+moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const float* __restrict__ corr, int T, int W,
+                 int E, int S, int groups, int keep, int top, float scale, int score_kind, int* idx, float* wt,
+                 float* gate_out) {
+  extern __shared__ float rs[];
+  const int R = E + S;
+  float* xs = rs;                                  // [RT_TOK][RT_KC]
+  float* z = xs + RT_TOK * RT_KC;                  // [RT_TOK][R]   logits, then scores
+  float* c = z + RT_TOK * R;                       // [RT_TOK][E]   choice scores
+  float* gs = c + RT_TOK * E;                      // [RT_TOK][groups] group scores
+  float* gk = gs + RT_TOK * groups;                // [RT_TOK][groups] 1: the group is kept
+  pdl_wait();
+  pdl_trigger();
+  const int t0 = blockIdx.x * RT_TOK;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < RT_TOK * R; i += blockDim.x) z[i] = 0.0f;
+  for (int k0 = 0; k0 < W; k0 += RT_KC) {
+    const int kc = min(RT_KC, W - k0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < RT_TOK * RT_KC; i += blockDim.x) {
+      const int tok = i / RT_KC, col = i - tok * RT_KC;
+      xs[i] = (t0 + tok < T && col < kc) ? moe_ld(x + (int64_t)(t0 + tok) * ldx + k0 + col) : 0.0f;
+    }
+    __syncthreads();
+    for (int e = warp; e < R; e += RT_TOK) {
+      const float* wrow = wr + (int64_t)e * W + k0;
+      float part[RT_TOK];
+#pragma unroll
+      for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = 0.0f;
+      for (int col = lane; col < kc; col += 32) {
+        const float w = wrow[col];
+#pragma unroll
+        for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = fmaf(w, xs[tok * RT_KC + col], part[tok]);
+      }
+#pragma unroll
+      for (int tok = 0; tok < RT_TOK; ++tok) {
+        const float s = warp_sum(part[tok]);
+        if (lane == 0) z[tok * R + e] += s;
+      }
+    }
+  }
+  __syncthreads();
+  const int t = t0 + warp;                         // this warp's token
+  if (t >= T) return;
+  float* zt = z + warp * R;
+  float* ct = c + warp * E;
+  float* gst = gs + warp * groups;
+  float* gkt = gk + warp * groups;
+  if (S && lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-zt[E]));
+  if (score_kind == 0) {
+    float mx = -INFINITY;
+    for (int e = lane; e < E; e += 32) mx = fmaxf(mx, zt[e]);
+    mx = warp_max(mx);
+    float sum = 0.0f;
+    for (int e = lane; e < E; e += 32) {
+      const float p = expf(zt[e] - mx);
+      ct[e] = p;
+      sum += p;
+    }
+    sum = warp_sum(sum);
+    for (int e = lane; e < E; e += 32) {
+      const float s = ct[e] / sum;
+      zt[e] = s;
+      ct[e] = s + corr[e];
+    }
+  } else {
+    for (int e = lane; e < E; e += 32) {
+      const float s = 1.0f / (1.0f + expf(-zt[e]));
+      zt[e] = s;
+      ct[e] = s + corr[e];
+    }
+  }
+  __syncwarp();
+  if (groups > 1 && keep < groups) {
+    const int per = E / groups;
+    for (int g = lane; g < groups; g += 32) {
+      float m = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, ct[e]);
+      gst[g] = m;
+      gkt[g] = 0.0f;
+    }
+    __syncwarp();
+    for (int r = 0; r < keep; ++r) {
+      float bv = -INFINITY;
+      int bi = 0x7fffffff;
+      for (int g = lane; g < groups; g += 32)
+        if (gkt[g] == 0.0f) arg_better(bv, bi, gst[g], g);
+      warp_argmax(bv, bi);
+      if (lane == 0 && bi < groups) gkt[bi] = 1.0f;
+      __syncwarp();
+    }
+    for (int e = lane; e < E; e += 32)
+      if (gkt[e / per] == 0.0f) ct[e] = -INFINITY;   // not 0: choice scores may be negative
+    __syncwarp();
+  }
+  for (int r = 0; r < top; ++r) {
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32)
+      if (ct[e] > -INFINITY) arg_better(bv, bi, ct[e], e);
+    warp_argmax(bv, bi);
+    if (lane == 0) {
+      if (bi < E) {
+        idx[(int64_t)t * top + r] = bi;
+        wt[(int64_t)t * top + r] = zt[bi] * scale;
+        ct[bi] = -INFINITY;
+      } else {
+        idx[(int64_t)t * top + r] = -1;
+        wt[(int64_t)t * top + r] = 0.0f;
+      }
+    }
+    __syncwarp();
+  }
+}
+
+// One block.  plan[0]: number of tiles; then per tile (expert, first place in `order`, rows), from plan[4] on.
+__global__ void __launch_bounds__(1024)
+moe_plan_kernel(const int* idx, int P, int n_experts, int* order, int* plan) {
+  extern __shared__ int ps[];                      // counts, offsets, cursors
+  int* counts = ps;
+  int* offs = ps + n_experts;
+  int* cursor = offs + n_experts;
+  pdl_wait();
+  pdl_trigger();
+  for (int e = threadIdx.x; e < n_experts; e += blockDim.x) { counts[e] = 0; cursor[e] = 0; }
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = __ldcg(idx + p);
+    if (e >= 0 && e < n_experts) atomicAdd(&counts[e], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int off = 0, nt = 0;
+    for (int e = 0; e < n_experts; ++e) {
+      offs[e] = off;
+      for (int r = 0; r < counts[e]; r += MOE_TM) {
+        plan[4 + 3 * nt] = e;
+        plan[5 + 3 * nt] = off + r;
+        plan[6 + 3 * nt] = min(MOE_TM, counts[e] - r);
+        ++nt;
+      }
+      off += counts[e];
+    }
+    plan[0] = nt;
+  }
+  __syncthreads();
+  for (int p = threadIdx.x; p < P; p += blockDim.x) {
+    const int e = __ldcg(idx + p);
+    if (e >= 0 && e < n_experts) order[offs[e] + atomicAdd(&cursor[e], 1)] = p;
+  }
+}
+
+__device__ inline float moe_act(float v, int act) {
+  if (act == 1) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
+  if (act == 2) return 0.5f * v * (1.0f + tanhf(0.79788456080286536f * (v + 0.044715f * v * v * v)));
+  if (act == 3) return v / (1.0f + expf(-v));
+  return v;
+}
+
+// out[p, n] = act(sum_k A[p / a_div, k] * W[e(p), n, k]) for the pairs p of the block's tile.
+template <typename TA, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const TA* A, int64_t lda, int a_div, const TW* __restrict__ Wt, const int* order, const int* plan,
+                TO* out, int N, int K, int act) {
+  __shared__ float As[MOE_TK][MOE_TM + 1];
+  __shared__ float Ws[MOE_TK][MOE_TN + 1];
+  __shared__ int rows[MOE_TM];
+  pdl_wait();
+  pdl_trigger();
+  const int tile = blockIdx.x;
+  if (tile >= __ldcg(plan)) return;
+  const int e = __ldcg(plan + 4 + 3 * tile), start = __ldcg(plan + 5 + 3 * tile), nrows = __ldcg(plan + 6 + 3 * tile);
+  const int n0 = blockIdx.y * MOE_TN;
+  if (threadIdx.x < MOE_TM) rows[threadIdx.x] = threadIdx.x < nrows ? __ldcg(order + start + threadIdx.x) : -1;
+  __syncthreads();
+  const TW* Wexp = Wt + (int64_t)e * N * K;
+  const int ty = threadIdx.x >> 4, tx = threadIdx.x & 15;       // rows ty * 2 .. + 1, columns tx * 4 .. + 3
+  float acc[2][4];
+#pragma unroll
+  for (int i = 0; i < 2; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.0f;
+  const int lk = threadIdx.x & 31, lr = threadIdx.x >> 5;       // loads: 32 consecutive k, 8 rows a pass
+  for (int k0 = 0; k0 < K; k0 += MOE_TK) {
+#pragma unroll
+    for (int r = lr; r < MOE_TM; r += 8) {
+      const int p = rows[r];
+      As[lk][r] = (p >= 0 && k0 + lk < K) ? moe_ld(A + (int64_t)(p / a_div) * lda + k0 + lk) : 0.0f;
+    }
+#pragma unroll
+    for (int r = lr; r < MOE_TN; r += 8) {
+      const int n = n0 + r;
+      Ws[lk][r] = (n < N && k0 + lk < K) ? moe_ld(Wexp + (int64_t)n * K + k0 + lk) : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int k = 0; k < MOE_TK; ++k) {
+      const float a0 = As[k][ty * 2], a1 = As[k][ty * 2 + 1];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float w = Ws[k][tx * 4 + j];
+        acc[0][j] = fmaf(a0, w, acc[0][j]);
+        acc[1][j] = fmaf(a1, w, acc[1][j]);
+      }
+    }
+    __syncthreads();
+  }
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    const int p = rows[ty * 2 + i];
+    if (p < 0) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) moe_st(out + (int64_t)p * N + n, moe_act(acc[i][j], act));
+    }
+  }
+}
+
+template <typename TX>
+__global__ void __launch_bounds__(256)
+moe_combine_kernel(const float* y, const int* idx, const float* wt, const TX* x, int64_t ldx, const void* shared,
+                   int shared_dtype, const float* gate, float* out, int T, int H, int top, int n_experts) {
+  pdl_wait();
+  pdl_trigger();
+  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (int64_t)T * H) return;
+  const int t = (int)(i / H), col = (int)(i - (int64_t)t * H);
+  float acc = 0.0f;
+  for (int k = 0; k < top; ++k) {
+    const int e = __ldcg(idx + (int64_t)t * top + k);
+    if (e < 0) continue;
+    const float w = __ldcg(wt + (int64_t)t * top + k);
+    const float v = e >= n_experts ? moe_ld(x + (int64_t)t * ldx + col) : __ldcg(y + ((int64_t)t * top + k) * H + col);
+    acc = fmaf(w, v, acc);
+  }
+  if (shared) {
+    const float s = shared_dtype == DT_F32 ? __ldcg(static_cast<const float*>(shared) + i)
+                                           : __bfloat162float(__ldcg(static_cast<const __nv_bfloat16*>(shared) + i));
+    acc = gate ? fmaf(__ldcg(gate + t), s, acc) : acc + s;
+  }
+  out[i] = acc;
+}
+
+}  // namespace exl3
+
+using namespace exl3;
+
+extern "C" int exl3_moe_tile_rows() { return MOE_TM; }
+
+extern "C" int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const float* wr, const float* corr, int T, int W,
+                              int E, int extra, int groups, int keep, int top, float scale, int score_kind, int* idx,
+                              float* wt, float* gate_out, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || W < 1 || E < 1 || extra < 0 || extra > 1 || groups < 1 || E % groups != 0 || keep < 1 || keep > groups ||
+      top < 1 || top > keep * (E / groups) || (extra && gate_out == nullptr) || score_kind < 0 || score_kind > 1) {
+    set_error("moe_route: bad sizes T=%d width=%d outputs=%d groups=%d keep=%d top=%d", T, W, E, groups, keep, top);
+    return ERR_BAD_ARGUMENT;
+  }
+  const size_t smem = (size_t)RT_TOK * (RT_KC + (E + extra) + E + 2 * groups) * sizeof(float);
+  if (smem > 200 * 1024) { set_error("moe_route: %d router outputs are too many", E); return ERR_UNSUPPORTED; }
+  void (*kernel)(const float*, int64_t, const float*, const float*, int, int, int, int, int, int, int, float, int, int*,
+                 float*, float*) = moe_route_kernel<float>;
+  void (*kernel_h)(const __nv_bfloat16*, int64_t, const float*, const float*, int, int, int, int, int, int, int, float,
+                   int, int*, float*, float*) = moe_route_kernel<__nv_bfloat16>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = x_dtype == DT_F32
+                        ? cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
+                        : cudaFuncSetAttribute(kernel_h, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_error("moe_route: shared memory refused: %s", cudaGetErrorString(e)); return (int)e; }
+  }
+  const dim3 grid(ceil_div(T, RT_TOK)), threads(RT_TOK * 32);
+  if (x_dtype == DT_F32)
+    launch_pdl(kernel, grid, threads, smem, stream, static_cast<const float*>(x), ldx, wr, corr, T, W, E, extra, groups,
+               keep, top, scale, score_kind, idx, wt, gate_out);
+  else if (x_dtype == DT_BF16)
+    launch_pdl(kernel_h, grid, threads, smem, stream, static_cast<const __nv_bfloat16*>(x), ldx, wr, corr, T, W, E, extra,
+               groups, keep, top, scale, score_kind, idx, wt, gate_out);
+  else { set_error("moe_route: unsupported element type %d", x_dtype); return ERR_UNSUPPORTED; }
+  return launch_status("moe_route");
+}
+
+extern "C" int exl3_moe_plan(const int* idx, int P, int n_experts, int* order, int* plan, cudaStream_t stream) {
+  if (P == 0) return 0;
+  if (P < 0 || n_experts < 1 || n_experts > 4096) { set_error("moe_plan: bad sizes"); return ERR_BAD_ARGUMENT; }
+  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), (size_t)3 * n_experts * sizeof(int), stream, idx, P, n_experts, order,
+             plan);
+  return launch_status("moe_plan");
+}
+
+// The most tiles a step of P pairs over n_experts experts can have.
+extern "C" int exl3_moe_max_tiles(int P, int n_experts) { return min(P, P / MOE_TM + n_experts); }
+
+template <typename TA, typename TW, typename TO>
+static int moe_gemm_launch(const void* A, int64_t lda, int a_div, const void* W, const int* order, const int* plan,
+                           void* out, int P, int n_experts, int N, int K, int act, cudaStream_t stream) {
+  const dim3 grid(exl3_moe_max_tiles(P, n_experts), ceil_div(N, MOE_TN));
+  launch_pdl(moe_gemm_kernel<TA, TW, TO>, grid, dim3(256), 0, stream, static_cast<const TA*>(A), lda, a_div,
+             static_cast<const TW*>(W), order, plan, static_cast<TO*>(out), N, K, act);
+  return launch_status("moe_gemm");
+}
+
+extern "C" int exl3_moe_gemm(const void* A, int a_dtype, int64_t lda, int a_div, const void* W, int w_dtype,
+                             const int* order, const int* plan, void* out, int out_dtype, int P, int n_experts, int N,
+                             int K, int act, cudaStream_t stream) {
+  if (P == 0) return 0;
+  if (P < 0 || n_experts < 1 || N < 1 || K < 1 || a_div < 1 || act < 0 || act > 3) {
+    set_error("moe_gemm: bad sizes pairs=%d experts=%d N=%d K=%d", P, n_experts, N, K);
+    return ERR_BAD_ARGUMENT;
+  }
+  if (ceil_div(N, MOE_TN) > 65535) { set_error("moe_gemm: grid too large"); return ERR_UNSUPPORTED; }
+#define EXL3_MOE(TA, DA, TW, DW, TO, DO)                                                                     \
+  if (a_dtype == DA && w_dtype == DW && out_dtype == DO)                                                     \
+    return moe_gemm_launch<TA, TW, TO>(A, lda, a_div, W, order, plan, out, P, n_experts, N, K, act, stream);
+  EXL3_MOE(float, DT_F32, float, DT_F32, float, DT_F32)
+  EXL3_MOE(__nv_bfloat16, DT_BF16, __nv_bfloat16, DT_BF16, __nv_bfloat16, DT_BF16)
+  EXL3_MOE(__nv_bfloat16, DT_BF16, __nv_bfloat16, DT_BF16, float, DT_F32)
+  EXL3_MOE(float, DT_F32, __nv_bfloat16, DT_BF16, float, DT_F32)
+  EXL3_MOE(float, DT_F32, __nv_bfloat16, DT_BF16, __nv_bfloat16, DT_BF16)
+#undef EXL3_MOE
+  set_error("moe_gemm: unsupported element types %d x %d -> %d", a_dtype, w_dtype, out_dtype);
+  return ERR_UNSUPPORTED;
+}
+
+extern "C" int exl3_moe_combine(const float* y, const int* idx, const float* wt, const void* x, int x_dtype, int64_t ldx,
+                                const void* shared, int shared_dtype, const float* gate, float* out, int T, int H,
+                                int top, int n_experts, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || H < 1 || top < 1) { set_error("moe_combine: bad sizes"); return ERR_BAD_ARGUMENT; }
+  const int64_t blocks = ((int64_t)T * H + 255) / 256;
+  if (blocks > 0x7fffffffLL) { set_error("moe_combine: too many elements"); return ERR_UNSUPPORTED; }
+  if (x_dtype == DT_F32)
+    launch_pdl(moe_combine_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, y, idx, wt,
+               static_cast<const float*>(x), ldx, shared, shared_dtype, gate, out, T, H, top, n_experts);
+  else if (x_dtype == DT_BF16)
+    launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, y, idx, wt,
+               static_cast<const __nv_bfloat16*>(x), ldx, shared, shared_dtype, gate, out, T, H, top, n_experts);
+  else { set_error("moe_combine: unsupported element type %d", x_dtype); return ERR_UNSUPPORTED; }
+  return launch_status("moe_combine");
+}

@@ -38,6 +38,10 @@ def plan_manifest(plan: ModelPlan) -> List[TensorSpec]:
                                                                              layer.names["feed_forward"])
             specs += norm_class(layer.feed_forward_norm.kind).tensor_specs(layer.feed_forward_norm,
                                                                           layer.names["feed_forward_norm"])
+    for layer in plan.layers:
+        arrangement = arrangement_class(layer.arrangement)
+        if hasattr(arrangement, "tensor_specs"):            # arrangements with tensors of their own (layer scales)
+            specs += arrangement.tensor_specs(layer)
     specs += norm_class(plan.final_norm.kind).tensor_specs(plan.final_norm, plan.final_norm_name)
     specs += head_class(plan.head.kind).tensor_specs(plan.head)
     return specs
@@ -70,6 +74,8 @@ class Model:
                     outs[1] = norm_class(layer.feed_forward_out_norm.kind)(layer.feed_forward_out_norm, tensors,
                                                                            layer.names["feed_forward_out_norm"], ctx)
                 self.blocks.append(arrangement_class(layer.arrangement)(layer, mixer, ff, n1, n2, out_norms=tuple(outs)))
+            elif getattr(arrangement_class(layer.arrangement), "takes_tensors", False):
+                self.blocks.append(arrangement_class(layer.arrangement)(layer, mixer, ff, n1, n2, tensors=tensors))
             else:
                 self.blocks.append(arrangement_class(layer.arrangement)(layer, mixer, ff, n1, n2))
         self.final_norm = norm_class(plan.final_norm.kind)(plan.final_norm, tensors, plan.final_norm_name, ctx)
@@ -103,7 +109,11 @@ class Model:
         for i, e in enumerate(sched):
             block = self.blocks[e.layer]
             kv, state = cache.view(i, batch.block_tables), cache.state_of(i)
-            if getattr(block, "takes_after", False):
+            if getattr(block, "takes_next", False):
+                # the block that runs next, so that this block's last kernel may also apply that block's first norms
+                block.forward(stream, batch, kv, state,
+                              next_block=self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None)
+            elif getattr(block, "takes_after", False):
                 # the norm that the next block applies first, so that this block's last projection may apply it
                 nxt = self.blocks[sched[i + 1].layer] if i + 1 < len(sched) else None
                 block.forward(stream, batch, kv, state, after=getattr(nxt, "mixer_norm", None))

@@ -106,16 +106,20 @@ def add_rmsnorm(h: torch.Tensor, y: Optional[torch.Tensor], y_scale: float, weig
     return out
 
 
-def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interleave: int = 0) -> torch.Tensor:
-    """``silu(gate) * up``.  ``interleave`` 0: ``gate_up = [gate | up]``; 8: eight
-    gate columns, then the eight up columns of the same features, and so on."""
+GATE_ACTIVATIONS = {"silu": 0, "gelu": 1, "gelu_tanh": 2}
+
+
+def silu_mul(gate_up: torch.Tensor, out: Optional[torch.Tensor] = None, interleave: int = 0,
+             act: str = "silu") -> torch.Tensor:
+    """``act(gate) * up`` (``act``: ``silu``, ``gelu`` by erf or ``gelu_tanh``).  ``interleave`` 0: ``gate_up =
+    [gate | up]``; 8: eight gate columns, then the eight up columns of the same features, and so on."""
     T, I2 = gate_up.shape
     I = I2 // 2
     _contig(gate_up, "gate_up")
     if out is None:
         out = torch.empty((T, I), dtype=gate_up.dtype, device=gate_up.device)
-    _check(library().exl3_silu_mul(_ptr(gate_up), _ptr(out), _c_int(dtype_code(gate_up.dtype)), _c_int(T),
-                                   _c_int(I), _c_int(interleave), _stream()), "silu_mul")
+    _check(library().exl3_act_mul(_ptr(gate_up), _ptr(out), _c_int(dtype_code(gate_up.dtype)), _c_int(T),
+                                  _c_int(I), _c_int(interleave), _c_int(GATE_ACTIVATIONS[act]), _stream()), "silu_mul")
     return out
 
 
@@ -521,12 +525,14 @@ def attn_tokens_ex(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool
     """``attn_tokens`` in its general form: rows of the key pool hold ``head_dim`` features and rows of the value
     pool ``value_dim`` (each pool's last dimension is its row pitch; multiples of 8; values may be wider than keys);
     ``chunk`` > 0 also hides every key before ``floor(pos / chunk) * chunk``; ``sink`` adds one to the softmax's
-    denominator.  ``out`` is ``[T, heads, value_dim]`` and the scratch is sized with ``value_dim``."""
-    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
+    denominator.  ``out`` is ``[T, heads, value_dim]`` in the cache's type or float32 (for callers that go on in
+    float32) and the scratch is sized with ``value_dim``."""
+    if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype not in (q.dtype, torch.float32):
         raise KernelLibraryError("attn_tokens_ex: q, cache and out differ in element type")
     nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
-    _check(library().exl3_attn_tokens_ex(
-        _ptr(q), _c_int64(q_row_stride), _ptr(out), _c_int(dtype_code(q.dtype)), _ptr(k_pool), _ptr(v_pool),
+    _check(library().exl3_attn_tokens_wide(
+        _ptr(q), _c_int64(q_row_stride), _ptr(out), _c_int(1 if out.dtype == torch.float32 else 0),
+        _c_int(dtype_code(q.dtype)), _ptr(k_pool), _ptr(v_pool),
         _ptr(block_table), _c_int(block_table.stride(0)), _ptr(tok_pos), _ptr(tok_seq), _c_int(T),
         _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(value_dim), _c_int(k_pool.shape[-1]),
         _c_int(v_pool.shape[-1]), _c_int(page), _c_int(window), _c_int(chunk), _c_int(1 if sink else 0),
@@ -622,11 +628,12 @@ def linear_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, st
                 slot_ids: torch.Tensor, row_start: torch.Tensor, rows: int, heads: int, dk: int, dv: int, max_new: int,
                 wraw: Optional[torch.Tensor] = None, w0: Optional[torch.Tensor] = None,
                 u: Optional[torch.Tensor] = None, decay: Optional[torch.Tensor] = None,
-                scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
+                scratch: Optional[torch.Tensor] = None, in_act: str = "none") -> torch.Tensor:
     """The recurrence with a matrix state per head over a step's packed tokens (see linear_scan.cu).  ``r``, ``k``
     ``[T, heads * dk]`` and ``v [T, heads * dv]`` may be views with their own row pitch; ``state`` float32 ``[slots,
     heads, dk, dv]`` is read and written at ``slot_ids``.  Mode 0: decays ``exp(-exp(wraw + w0))`` per token and key
-    channel and the bonus ``u``; mode 1: ``decay`` float32 ``[heads]``.  Returns float32 ``[T, heads * dv]``."""
+    channel and the bonus ``u``; mode 1: ``decay`` float32 ``[heads]``.  ``in_act`` ``"silu"``: ``r``, ``k`` and ``v`` go
+    through SiLU (float32) as they are read.  Returns float32 ``[T, heads * dv]``."""
     T = r.shape[0]
     for t, name in ((r, "r"), (k, "k"), (v, "v"), (wraw, "wraw")):
         if t is not None and t.stride(1) != 1:
@@ -647,15 +654,15 @@ def linear_scan(mode: int, r: torch.Tensor, k: torch.Tensor, v: torch.Tensor, st
         _c_int64(wraw.stride(0) if wraw is not None else 0), _c_int(dtype_code(wraw.dtype) if wraw is not None else 0),
         _ptr(w0), _ptr(u), _c_int(dtype_code(w0.dtype) if w0 is not None else 0), _ptr(decay), _ptr(state),
         _ptr(slot_ids), _ptr(row_start), _ptr(out), _c_int(rows), _c_int(T), _c_int(heads), _c_int(dk), _c_int(dv),
-        _c_int(max_new), _ptr(scratch),
+        _c_int(max_new), _c_int({"none": 0, "silu": 1}[in_act]), _ptr(scratch),
         _c_size_t(0 if scratch is None else scratch.numel() * scratch.element_size()), _stream()), "linear_scan")
     return out
 
 
 def head_norm_gate(o: torch.Tensor, w: Optional[torch.Tensor], gate: Optional[torch.Tensor], eps: float, heads: int,
-                   dv: int, out_dtype: torch.dtype) -> torch.Tensor:
+                   dv: int, out_dtype: torch.dtype, gate_kind: str = "silu") -> torch.Tensor:
     """``o [T, heads * dv]`` (float32) head by head divided by its root mean square, times ``w [heads * dv]`` and
-    ``silu(gate [T, heads * dv])`` where given."""
+    ``silu(gate [T, heads * dv])`` (``gate_kind`` ``"sigmoid"``: the sigmoid alone) where given."""
     T = o.shape[0]
     _contig(o, "o")
     if o.dtype != torch.float32 or o.shape[1] != heads * dv:
@@ -666,8 +673,8 @@ def head_norm_gate(o: torch.Tensor, w: Optional[torch.Tensor], gate: Optional[to
     _check(library().exl3_head_norm_gate(
         _ptr(o), _ptr(w), _c_int(dtype_code(w.dtype) if w is not None else 0), _ptr(gate),
         _c_int(dtype_code(gate.dtype) if gate is not None else 0), _c_int64(gate.stride(0) if gate is not None else 0),
-        _c_float(eps), _ptr(out), _c_int(dtype_code(out.dtype)), _c_int(T), _c_int(heads), _c_int(dv), _stream()),
-        "head_norm_gate")
+        _c_int({"silu": 0, "sigmoid": 1}[gate_kind]), _c_float(eps), _ptr(out), _c_int(dtype_code(out.dtype)), _c_int(T),
+        _c_int(heads), _c_int(dv), _stream()), "head_norm_gate")
     return out
 
 
@@ -1054,3 +1061,177 @@ def sample_count(counts: torch.Tensor, ids: torch.Tensor, vocab: int) -> None:
         raise KernelLibraryError("sample_count: counts int64 [R] and ids int32 [R]")
     _check(library().exl3_sample_count(_ptr(counts), _ptr(ids), _c_int(ids.numel()), _c_int(vocab), _stream()),
            "sample_count")
+
+
+# -- a norm without statistics, side-by-side sublayers, routed feed-forwards, heads of several maps -------------------
+
+def tanh_norm_add(h: torch.Tensor, a: Optional[torch.Tensor], b: Optional[torch.Tensor], sa: Optional[torch.Tensor],
+                  sb: Optional[torch.Tensor], m: float, norms, out_dtype: torch.dtype,
+                  rows: Optional[torch.Tensor] = None):
+    """The residual step of layers whose sublayers read the same residual, and up to two norms of the kind
+    ``tanh(alpha x) w + b`` over the result (see tanh_norm.cu).  With ``a`` given: ``h += m * (sa * a + sb * b)`` in
+    place (``b`` may be None).  ``norms``: up to two ``(w, b, alpha)`` triples of float32 tensors; returns the list
+    of their outputs ``[T, H]`` in ``out_dtype``.  With ``rows`` (and no ``a``) only those rows are normed."""
+    T, H = h.shape
+    if h.dtype != torch.float32:
+        raise KernelLibraryError("tanh_norm_add: the residual stream must be float32")
+    _contig(h, "h")
+    for t, name in ((a, "a"), (b, "b")):
+        if t is not None:
+            _contig(t, name)
+            if t.shape != h.shape:
+                raise KernelLibraryError(f"tanh_norm_add: {name} is {tuple(t.shape)}, h is {tuple(h.shape)}")
+    if len(norms) > 2:
+        raise KernelLibraryError("tanh_norm_add: at most two norms")
+    for w, bias, alpha in norms:
+        if any(x.dtype != torch.float32 for x in (w, bias, alpha)) or w.numel() != H or bias.numel() != H:
+            raise KernelLibraryError("tanh_norm_add: a norm's weight, bias and alpha must be float32 of the row's width")
+    for s_, name in ((sa, "sa"), (sb, "sb")):
+        if s_ is not None and (s_.dtype != torch.float32 or s_.numel() != H):
+            raise KernelLibraryError(f"tanh_norm_add: {name} must be float32 of the row's width")
+    n = T if rows is None else rows.numel()
+    if rows is not None and rows.dtype != torch.int32:
+        raise KernelLibraryError("tanh_norm_add: rows must be int32")
+    outs = [torch.empty((n, H), dtype=out_dtype, device=h.device) for _ in norms]
+    args = []
+    for i in range(2):
+        if i < len(norms):
+            w, bias, alpha = norms[i]
+            args += [_ptr(w), _ptr(bias), _ptr(alpha), _ptr(outs[i])]
+        else:
+            args += [_c_void_p(0)] * 4
+    _check(library().exl3_tanh_norm_add(
+        _ptr(h), _ptr(a), _c_int(dtype_code(a.dtype) if a is not None else 0), _ptr(b),
+        _c_int(dtype_code(b.dtype) if b is not None else 0), _ptr(sa), _ptr(sb), _c_float(m), _ptr(rows), _c_int(n),
+        *args, _c_int(dtype_code(out_dtype)), _c_int(T), _c_int(H), _stream()), "tanh_norm_add")
+    return outs
+
+
+def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
+    """``x <- cap * tanh(x / cap)`` in place (float32)."""
+    _contig(x, "x")
+    if x.dtype != torch.float32:
+        raise KernelLibraryError("softcap: float32 only")
+    _check(library().exl3_softcap(_ptr(x), _c_int64(x.numel()), _c_float(cap), _stream()), "softcap")
+    return x
+
+
+MOE_ACTIVATIONS = {"none": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3}
+MOE_SCORES = {"softmax": 0, "sigmoid": 1}
+
+
+def moe_max_tiles(pairs: int, n_experts: int) -> int:
+    return int(library().exl3_moe_max_tiles(_c_int(pairs), _c_int(n_experts)))
+
+
+def moe_route(x: torch.Tensor, wr: torch.Tensor, corr: torch.Tensor, outputs: int, extra: int, groups: int, keep: int,
+              top: int, scale: float, score: str = "softmax"):
+    """The router of a routed feed-forward (see moe.cu): ``wr`` float32 ``[outputs + extra, W]``, ``corr`` float32
+    ``[outputs]`` added to the scores for the choice only.  Returns ``(idx int32 [T, top], weight float32 [T, top],
+    gate float32 [T] or None)``: the gate is the sigmoid of the extra row's product."""
+    T, W = x.shape
+    if x.stride(1) != 1:
+        raise KernelLibraryError("moe_route: rows of x must be dense")
+    _contig(wr, "wr")
+    if wr.dtype != torch.float32 or corr.dtype != torch.float32 or tuple(wr.shape) != (outputs + extra, W) or \
+            corr.numel() != outputs:
+        raise KernelLibraryError("moe_route: the router's matrix and correction must be float32 [outputs (+ 1), W] and [outputs]")
+    idx = torch.empty((T, top), dtype=torch.int32, device=x.device)
+    wt = torch.empty((T, top), dtype=torch.float32, device=x.device)
+    gate = torch.empty((T,), dtype=torch.float32, device=x.device) if extra else None
+    _check(library().exl3_moe_route(
+        _ptr(x), _c_int(dtype_code(x.dtype)), _c_int64(x.stride(0)), _ptr(wr), _ptr(corr), _c_int(T), _c_int(W),
+        _c_int(outputs), _c_int(extra), _c_int(groups), _c_int(keep), _c_int(top), _c_float(scale),
+        _c_int(MOE_SCORES[score]), _ptr(idx), _ptr(wt), _ptr(gate), _stream()), "moe_route")
+    return idx, wt, gate
+
+
+def moe_plan(idx: torch.Tensor, n_experts: int):
+    """Orders a step's (token, pick) pairs by expert and cuts them into tiles, on the device.  Returns ``(order int32
+    [pairs], plan int32)`` for ``moe_gemm``; picks outside ``0 .. n_experts - 1`` (identity outputs) are left out."""
+    _contig(idx, "idx")
+    P = idx.numel()
+    order = torch.empty((P,), dtype=torch.int32, device=idx.device)
+    plan = torch.empty((4 + 3 * max(1, moe_max_tiles(P, n_experts)),), dtype=torch.int32, device=idx.device)
+    _check(library().exl3_moe_plan(_ptr(idx), _c_int(P), _c_int(n_experts), _ptr(order), _ptr(plan), _stream()),
+           "moe_plan")
+    return order, plan
+
+
+def moe_gemm(a: torch.Tensor, a_div: int, w: torch.Tensor, order: torch.Tensor, plan: torch.Tensor,
+             out_dtype: torch.dtype, act: str = "none") -> torch.Tensor:
+    """``out[p] = act(w[expert(p)] a[p // a_div])`` for the planned pairs: ``w [experts, N, K]``; ``a [rows, K]`` has
+    one row per pair (``a_div`` 1) or per token (``a_div`` = picks per token).  Rows of pairs that are not planned
+    are left unwritten."""
+    E, N, Kd = w.shape
+    _contig(w, "w")
+    if a.stride(1) != 1 or a.shape[1] != Kd:
+        raise KernelLibraryError("moe_gemm: rows of a must be dense and as wide as the experts' inputs")
+    P = order.numel()
+    out = torch.empty((P, N), dtype=out_dtype, device=a.device)
+    _check(library().exl3_moe_gemm(
+        _ptr(a), _c_int(dtype_code(a.dtype)), _c_int64(a.stride(0)), _c_int(a_div), _ptr(w), _c_int(dtype_code(w.dtype)),
+        _ptr(order), _ptr(plan), _ptr(out), _c_int(dtype_code(out_dtype)), _c_int(P), _c_int(E), _c_int(N), _c_int(Kd),
+        _c_int(MOE_ACTIVATIONS[act]), _stream()), "moe_gemm")
+    return out
+
+
+def moe_combine(y: Optional[torch.Tensor], idx: torch.Tensor, wt: torch.Tensor, x: torch.Tensor,
+                shared: Optional[torch.Tensor], gate: Optional[torch.Tensor], n_experts: int) -> torch.Tensor:
+    """``out[t] = sum_k wt[t, k] * (y[t, k] or, for picks from ``n_experts`` on, x[t]) + gate[t] * shared[t]``,
+    float32 ``[T, H]``; ``y`` float32 ``[T * top, H]``."""
+    T, top = idx.shape
+    H = x.shape[1]
+    if x.stride(1) != 1:
+        raise KernelLibraryError("moe_combine: rows of x must be dense")
+    if y is not None and (y.dtype != torch.float32 or not y.is_contiguous()):
+        raise KernelLibraryError("moe_combine: the experts' outputs must be contiguous float32")
+    if shared is not None:
+        _contig(shared, "shared")
+    out = torch.empty((T, H), dtype=torch.float32, device=x.device)
+    _check(library().exl3_moe_combine(
+        _ptr(y), _ptr(idx), _ptr(wt), _ptr(x), _c_int(dtype_code(x.dtype)), _c_int64(x.stride(0)), _ptr(shared),
+        _c_int(dtype_code(shared.dtype) if shared is not None else 0), _ptr(gate), _ptr(out), _c_int(T), _c_int(H),
+        _c_int(top), _c_int(n_experts), _stream()), "moe_combine")
+    return out
+
+
+def maps_prep(x: torch.Tensor, q_off: int, k_off: int, v_off: int, heads: int, kv_heads: int, maps: int, d: int,
+              dv: int, rot: int, inv_freq: Optional[torch.Tensor], tok_pos: torch.Tensor, tok_seq: torch.Tensor,
+              block_table: torch.Tensor, page: int, q_dtype: torch.dtype, k_pool: torch.Tensor,
+              v_pool: torch.Tensor) -> torch.Tensor:
+    """What stands between the joint projection ``x [T, ld]`` of an attention whose heads hold ``maps`` maps and
+    the attention kernels (see diff_attn.cu): half-split rotation of the first ``rot`` features of every map, the
+    cache write (a key row holds the kv head's maps side by side, the pools' last dimensions are the row pitches)
+    and the queries widened to one head per map: returns ``[T, heads * maps, key row]``."""
+    T = x.shape[0]
+    if x.stride(1) != 1:
+        raise KernelLibraryError("maps_prep: rows of x must be dense")
+    row, v_row = k_pool.shape[-1], v_pool.shape[-1]
+    hi, lo = (_rotary_rows(inv_freq, rot, "maps_prep") if rot else (_c_void_p(0), _c_void_p(0)))
+    q = torch.empty((T, heads * maps * row), dtype=q_dtype, device=x.device)
+    _check(library().exl3_maps_prep(
+        _ptr(x), _c_int(dtype_code(x.dtype)), _c_int64(x.stride(0)), _c_int(q_off), _c_int(k_off), _c_int(v_off),
+        _c_int(T), _c_int(heads), _c_int(kv_heads), _c_int(maps), _c_int(d), _c_int(dv), _c_int(row), _c_int(v_row),
+        _c_int(rot), hi, lo, _ptr(tok_pos), _ptr(tok_seq), _ptr(block_table), _c_int(block_table.stride(0)),
+        _c_int(page), _ptr(q), _c_int(dtype_code(q_dtype)), _ptr(k_pool), _ptr(v_pool),
+        _c_int(dtype_code(k_pool.dtype)), _stream()), "maps_prep")
+    return q
+
+
+def diff_combine(a: torch.Tensor, a_row: int, gate: Optional[torch.Tensor], lam: float, eps: float, mult: float,
+                 heads: int, dv: int, out_row: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``o = a_0 - lam * a_1`` of every head's two maps (``a [T, heads * 2 * a_row]``), divided by its root mean
+    square over the head's ``dv`` values, times ``mult`` and ``sigmoid(gate[t, head])``; rows of ``out_row``
+    elements (zeros beyond ``dv``)."""
+    T = a.shape[0]
+    _contig(a, "a")
+    if gate is not None and gate.stride(1) != 1:
+        raise KernelLibraryError("diff_combine: rows of the gate must be dense")
+    out = torch.empty((T, heads * out_row), dtype=out_dtype, device=a.device)
+    _check(library().exl3_diff_combine(
+        _ptr(a), _c_int(dtype_code(a.dtype)), _c_int(a_row), _ptr(gate),
+        _c_int(dtype_code(gate.dtype) if gate is not None else 0), _c_int64(gate.stride(0) if gate is not None else 0),
+        _c_float(lam), _c_float(eps), _c_float(mult), _ptr(out), _c_int(dtype_code(out_dtype)), _c_int(out_row),
+        _c_int(T), _c_int(heads), _c_int(dv), _stream()), "diff_combine")
+    return out

@@ -1,6 +1,6 @@
 """Parts a layer is put together from, and their registries."""
-from . import (attention, block, embedding, ffn, latent_attention, linear_recurrence, norm, normed_attention, parallel,  # noqa: F401
-               position, recurrent)  # noqa: F401  (register the built-in parts)
+from . import (attention, block, diff_attention, embedding, ffn, latent_attention, linear_recurrence, moe, norm,  # noqa: F401
+               normed_attention, parallel, position, recurrent)  # noqa: F401  (register the built-in parts)
 from .base import BuildContext, KVRequest, ResidualStream, StateRequest
 from .registry import (arrangement_class, embedding_class, feed_forward_class, head_class, mixer_class, norm_class,
                        position_class, register_arrangement, register_embedding, register_feed_forward,

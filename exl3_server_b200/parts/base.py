@@ -90,6 +90,18 @@ class ResidualStream:
             return got[1]
         return None
 
+    def leave_for(self, norms, outputs) -> None:
+        """Leaves the outputs of several norms over the residual as it stands (a block whose sublayers read norms
+        of the same residual takes them with ``take_for``)."""
+        self.normed = (tuple(norms), list(outputs))
+
+    def take_for(self, norms):
+        got, self.normed = self.normed, None
+        if got is not None and self.pending is None and isinstance(got[0], tuple) and len(got[0]) == len(norms) \
+                and all(a is b for a, b in zip(got[0], norms)):
+            return got[1]
+        return None
+
     def take(self):
         y, s = self.pending, self.pending_scale
         self.pending, self.pending_scale = None, 1.0

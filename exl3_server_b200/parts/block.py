@@ -13,9 +13,22 @@ A layer of this kind may have no feed-forward at all.
 ``sandwich``: a norm on both sides of each sublayer: ``h += rho * norm1b(mixer(norm1(h)))`` then
 ``h += rho * norm2b(ff(norm2(h)))``.  The constant ``rho`` is a parameter of the output norms (their ``scale``), so
 the second norm, the constant and the add (float32) are one kernel, as in ``outnorm``.
+
+``side_by_side``: both sublayers read norms of the same residual and their outputs are added together, each times a
+learned vector of its own (a layer scale): ``h += rho * (s1 * mixer(norm1(h)) + s2 * ff(norm2(h)))``.  The step, in
+float32, and the two norms that the next block of this kind applies to the new residual are one kernel
+(``kernels.tanh_norm_add``) when those norms are of the ``tanh`` kind; other norms run as kernels of their own.  The
+vectors are tensors of the arrangement (names under ``mixer_scale`` and ``feed_forward_scale``).  A layer may have no
+feed-forward.
 """
 from __future__ import annotations
 
+from typing import Dict, List
+
+import torch
+
+from ..ops import kernels as K
+from ..weights.loader import TensorSpec
 from .base import NormAfter, ResidualStream
 from .registry import register_arrangement
 from .spec import LayerSpec
@@ -123,6 +136,64 @@ class SandwichBlock:
                    if p is not None and hasattr(p, "weight_bytes"))
 
 
+class SideBySideBlock:
+    takes_tensors = True      # built with the checkpoint's tensors (the layer-scale vectors)
+    takes_next = True         # forward gets the block that runs next
+
+    @staticmethod
+    def tensor_specs(spec: LayerSpec) -> List[TensorSpec]:
+        out = [TensorSpec(spec.names["mixer_scale"], (spec.mixer.width,), init="ones")]
+        if spec.feed_forward is not None:
+            out.append(TensorSpec(spec.names["feed_forward_scale"], (spec.mixer.width,), init="ones"))
+        return out
+
+    def __init__(self, spec: LayerSpec, mixer, feed_forward, mixer_norm, feed_forward_norm,
+                 tensors: Dict[str, torch.Tensor]):
+        self.spec = spec
+        self.mixer = mixer
+        self.feed_forward = feed_forward              # None: the layer is its mixer only
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm if feed_forward is not None else None
+        self.mixer_scale = tensors[spec.names["mixer_scale"]].float().contiguous()
+        self.feed_forward_scale = None
+        if feed_forward is not None:
+            self.feed_forward_scale = tensors[spec.names["feed_forward_scale"]].float().contiguous()
+
+    def input_norms(self):
+        """The norms this block applies to the residual it is given."""
+        return tuple(n for n in (self.mixer_norm, self.feed_forward_norm) if n is not None)
+
+    @staticmethod
+    def _normed(stream: ResidualStream, norms):
+        xs = stream.take_for(norms)
+        if xs is not None:
+            return xs
+        if all(hasattr(n, "tanh_args") for n in norms) and stream.pending is None:
+            return K.tanh_norm_add(stream.h, None, None, None, None, 1.0, [n.tanh_args() for n in norms],
+                                   norms[0].out_dtype)
+        return [n.add_norm(stream) for n in norms]
+
+    def forward(self, stream: ResidualStream, batch, kv, state, next_block=None) -> None:
+        xs = self._normed(stream, self.input_norms())
+        y1 = self.mixer.forward(xs[0], batch, kv, state)
+        y2 = self.feed_forward.forward(xs[1], batch) if self.feed_forward is not None else None
+        nxt = next_block.input_norms() if hasattr(next_block, "input_norms") else ()
+        fused = bool(nxt) and all(hasattr(n, "tanh_args") for n in nxt)
+        outs = K.tanh_norm_add(stream.h, y1, y2, self.mixer_scale, self.feed_forward_scale,
+                               float(self.spec.residual_scale), [n.tanh_args() for n in nxt] if fused else [],
+                               nxt[0].out_dtype if fused else torch.float32)
+        stream.act = None
+        stream.normed = None
+        if fused:
+            stream.leave_for(nxt, outs)
+
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in (self.mixer, self.feed_forward, self.mixer_norm, self.feed_forward_norm)
+                   if p is not None and hasattr(p, "weight_bytes")) + 4 * self.mixer_scale.numel() * \
+            (2 if self.feed_forward_scale is not None else 1)
+
+
 register_arrangement("prenorm", PreNormBlock)
+register_arrangement("side_by_side", SideBySideBlock)
 register_arrangement("sandwich", SandwichBlock)
 register_arrangement("outnorm", OutNormBlock)

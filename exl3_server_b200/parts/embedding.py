@@ -4,7 +4,7 @@ Embedding: ``h0[t] = E[id_t] * scale`` (the gather is src/model.cpp:529; the
 scale is MiniCPM's ``scale_emb``).  Head: ``logits = (norm(h) / divisor) W^T``
 in float32, computed only for the rows that were asked for (the reference
 computes every row, src/model.cpp:589-592); ``W`` is the embedding table when
-the head is tied.
+the head is tied.  With ``softcap`` c > 0 in the head's parameters the logits become ``c tanh(logits / c)``.
 
 Both are registered part kinds like the others (``"table"`` and ``"linear"``).  An embedding of another kind has
 ``tensor_specs(spec)``, ``__init__(spec, tensors, ctx)`` and ``forward(token_ids) -> ResidualStream``; a head has
@@ -59,7 +59,11 @@ class Head:
 
     def forward(self, stream: ResidualStream, final_norm, rows: Optional[torch.Tensor]) -> torch.Tensor:
         r = final_norm.add_norm(stream, rows=rows, out_scale=1.0 / float(self.spec.input_divisor))
-        return self.linear(r, out_dtype=torch.float32)
+        logits = self.linear(r, out_dtype=torch.float32)
+        cap = float(self.spec.params.get("softcap", 0.0))
+        if cap > 0.0:
+            K.softcap(logits, cap)              # logits <- cap * tanh(logits / cap)
+        return logits
 
     def weight_bytes(self) -> int:
         """Bytes this part holds beyond the embedding's."""

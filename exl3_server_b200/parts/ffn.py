@@ -11,6 +11,10 @@ inside its kernel.
 ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z/2`` otherwise; it is computed in
 float32 (from float32 results of the up projection where the projection's kernel has them); for steps of few
 tokens it is the epilogue of the up projection's weight-streaming kernel.
+
+``gated``: ``y = Wd (act(Wg r) * (Wu r))`` with the gate's activation named in ``params["activation"]`` (``silu``,
+``gelu`` or ``gelu_tanh``); tensors ``gate``, ``up``, ``down``.  Gate and up are one matrix; the product is float32
+inside its kernel.
 """
 from __future__ import annotations
 
@@ -154,5 +158,30 @@ class DenseFeedForward:
         return self.up.weight_bytes() + self.down.weight_bytes()
 
 
+class GatedFeedForward:
+    @staticmethod
+    def tensor_specs(spec: FeedForwardSpec, prefix: str) -> List[TensorSpec]:
+        return [TensorSpec(prefix + "gate", (spec.inner, spec.width)), TensorSpec(prefix + "up", (spec.inner, spec.width)),
+                TensorSpec(prefix + "down", (spec.width, spec.inner))]
+
+    def __init__(self, spec: FeedForwardSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
+        self.spec = spec
+        self.dtype = ctx.dtype
+        self.act = spec.params.get("activation", "silu")
+        if self.act not in K.GATE_ACTIVATIONS:
+            raise ValueError(f"gated feed-forward: no activation named {self.act!r}; known: {sorted(K.GATE_ACTIVATIONS)}")
+        self.gate_up = Linear(torch.cat([tensors[prefix + "gate"].to(ctx.dtype), tensors[prefix + "up"].to(ctx.dtype)],
+                                        dim=0), None, ctx.dtype)
+        self.down = Linear(tensors[prefix + "down"], None, ctx.dtype)
+
+    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+        T = x.shape[0]
+        return self.down(K.silu_mul(self.gate_up(x), act=self.act), out_dtype=self.down.wide_dtype(T))
+
+    def weight_bytes(self) -> int:
+        return self.gate_up.weight_bytes() + self.down.weight_bytes()
+
+
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("gated", GatedFeedForward)
 register_feed_forward("dense", DenseFeedForward)

@@ -20,6 +20,12 @@ the gate, then ``Wo``.  Parameters: ``key_dim`` (= value size), ``norm_eps``; th
 checkpoint has.  Tensors: ``mu.r``, ``mu.k``, ``mu.v``, ``mu.g``, ``mu.w``, ``r``, ``k``, ``v``, ``g``, ``w1``,
 ``w2``, ``w0``, ``u``, ``norm``, ``o``.
 
+``lightning``: the same chain as ``retention`` with activations in place of positions: ``q, k = silu(Wq r),
+silu(Wk r)`` (``heads x dk``), ``v = silu(Wv r)`` (``heads x dv``), no factor on the keys; ``S_t = decay_h S_(t-1) +
+k_t v_t^T``, ``o_t = S_t^T q_t``; the concatenated heads are divided by their root mean square TOGETHER and
+multiplied by a weight, then by ``sigmoid(Wg r)``, and projected by ``Wo``.  Parameters: ``key_dim``, ``value_dim``,
+``decay`` (one per head), ``norm_eps``.  Tensors: ``q``, ``k``, ``v``, ``g``, ``o``, ``norm``.
+
 Decays, their exponentials, the bonus, the state, the rotation and the per-head norms are float32; the projections
 are the model's type.
 """
@@ -108,6 +114,59 @@ class Retention:
         return self._w.numel() * self._w.element_size() + self.o.weight_bytes()
 
 
+class Lightning:
+    @staticmethod
+    def _sizes(spec: MixerSpec) -> Tuple[int, int, int]:
+        dk = int(spec.params["key_dim"])
+        return spec.heads, dk, int(spec.params.get("value_dim", 0)) or dk
+
+    @classmethod
+    def tensor_specs(cls, spec: MixerSpec, prefix: str) -> List[TensorSpec]:
+        H, dk, dv = cls._sizes(spec)
+        return [TensorSpec(prefix + "q", (H * dk, spec.width)), TensorSpec(prefix + "k", (H * dk, spec.width)),
+                TensorSpec(prefix + "v", (H * dv, spec.width)), TensorSpec(prefix + "g", (H * dv, spec.width)),
+                TensorSpec(prefix + "o", (spec.width, H * dv)), TensorSpec(prefix + "norm", (H * dv,), init="ones")]
+
+    def __init__(self, spec: MixerSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
+        H, dk, dv = self._sizes(spec)
+        decay = [float(x) for x in spec.params["decay"]]
+        if H < 1 or len(decay) != H:
+            raise ValueError(f"lightning: {len(decay)} decays for {H} heads")
+        self.spec, self.ctx = spec, ctx
+        self.H, self.dk, self.dv = H, dk, dv
+        self.eps = float(spec.params.get("norm_eps", 1e-6))
+        self.decay = torch.tensor(decay, dtype=torch.float64).to(torch.float32).to(ctx.device)
+        self.proj = Linear(torch.cat([tensors[prefix + n].to(ctx.dtype) for n in ("q", "k", "v", "g")], dim=0), None,
+                           ctx.dtype)
+        self.norm_w = tensors[prefix + "norm"].float().contiguous()
+        self.o = Linear(tensors[prefix + "o"], None, ctx.dtype)
+
+    def cache_request(self) -> Optional[KVRequest]:
+        return None
+
+    def state_request(self) -> Optional[StateRequest]:
+        return StateRequest((self.H, self.dk, self.dv), torch.float32)
+
+    def forward(self, x: torch.Tensor, batch, kv, state) -> torch.Tensor:
+        if state is None:
+            raise RuntimeError("lightning needs its per-sequence state")
+        H, dk, dv = self.H, self.dk, self.dv
+        T = x.shape[0]
+        proj = self.proj(x, out_dtype=self.proj.wide_dtype(T))
+        q, k = proj[:, :H * dk], proj[:, H * dk:2 * H * dk]
+        v = proj[:, 2 * H * dk:2 * H * dk + H * dv]
+        g = proj[:, 2 * H * dk + H * dv:]
+        # SiLU in float32 as the scan reads its inputs: what enters the recurrence is not rounded again
+        o = K.linear_scan(1, q, k, v, state, batch.slot_ids, batch.row_start, batch.n_rows, H, dk, dv, batch.max_new,
+                          decay=self.decay, scratch=_scan_scratch(batch, T, H, dk, dv), in_act="silu")
+        # all heads are normed together: one "head" of H * dv values
+        y = K.head_norm_gate(o, self.norm_w, g, self.eps, 1, H * dv, self.ctx.dtype, gate_kind="sigmoid")
+        return self.o(y, out_dtype=self.o.wide_dtype(T))
+
+    def weight_bytes(self) -> int:
+        return self.proj.weight_bytes() + self.o.weight_bytes()
+
+
 class WKV:
     BLENDS = ("r", "k", "v", "g", "w")
 
@@ -181,3 +240,4 @@ class WKV:
 
 register_mixer("retention", Retention)
 register_mixer("wkv", WKV)
+register_mixer("lightning", Lightning)

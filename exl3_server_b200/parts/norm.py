@@ -11,6 +11,10 @@ input (``add_normed``: ``h += rmsnorm(y) * w``; the ``outnorm`` and ``sandwich``
 Parameters of the spec: ``suffix`` (the tensor's name after the prefix), ``one_plus`` (the stored weight lies
 around zero and the factor is ``1 + w``) and ``scale`` (a constant on the norm's output, such as a multiplier of
 the residual branch).
+
+``tanh``: a norm that computes no statistics, ``r = tanh(alpha * h) * w + b`` with one learned number ``alpha`` and
+the vectors ``w`` and ``b`` (tensors: the prefix itself, or prefix + ``suffix``, for ``w``; that name + ``.b`` and
++ ``.alpha``).  Float32 throughout.  The spec's ``eps`` is not used.
 """
 from __future__ import annotations
 
@@ -94,4 +98,50 @@ class RMSNorm:
         return self.weight.numel() * self.weight.element_size()
 
 
+class DynamicTanhNorm:
+    @staticmethod
+    def _name(spec: NormSpec, prefix: str) -> str:
+        return prefix + spec.params.get("suffix", "")
+
+    @classmethod
+    def tensor_specs(cls, spec: NormSpec, prefix: str) -> List[TensorSpec]:
+        n = cls._name(spec, prefix)
+        return [TensorSpec(n, (spec.width,), init="ones"), TensorSpec(n + ".b", (spec.width,)),
+                TensorSpec(n + ".alpha", (), init="ones")]
+
+    def __init__(self, spec: NormSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
+        n = self._name(spec, prefix)
+        self.spec = spec
+        self.weight = tensors[n].float().contiguous()
+        self.bias = tensors[n + ".b"].float().contiguous()
+        self.alpha = tensors[n + ".alpha"].float().reshape(1).contiguous()
+        self.out_dtype = ctx.dtype
+        self._ones: Optional[torch.Tensor] = None
+
+    def tanh_args(self):
+        """``(w, b, alpha)`` for a kernel that applies this norm together with something else."""
+        return self.weight, self.bias, self.alpha
+
+    def add_norm(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, out_scale: float = 1.0,
+                 raw_ok: bool = False):
+        if out_scale != 1.0:
+            raise ValueError("tanh norm: no constant on the output (fold it into the weight and the bias)")
+        left = stream.take_normed(self)
+        if left is not None:
+            return left.materialize(1.0, rows)
+        y, s = stream.take()
+        if y is not None:
+            stream.act = None
+            if self._ones is None:
+                self._ones = torch.ones_like(self.weight)
+            if rows is None:
+                return K.tanh_norm_add(stream.h, y, None, self._ones, None, s, [self.tanh_args()], self.out_dtype)[0]
+            K.tanh_norm_add(stream.h, y, None, self._ones, None, s, [], self.out_dtype)
+        return K.tanh_norm_add(stream.h, None, None, None, None, 1.0, [self.tanh_args()], self.out_dtype, rows=rows)[0]
+
+    def weight_bytes(self) -> int:
+        return 4 * (self.weight.numel() + self.bias.numel() + 1)
+
+
 register_norm("rms", RMSNorm)
+register_norm("tanh", DynamicTanhNorm)
