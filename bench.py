@@ -27,8 +27,9 @@ the size tables and prints a short JSON line (for profiling small cases).
 
 ``--only designs`` measures the Rigitar decoder (latent attention, minGRU and
 dense xIELU layers) and the Nikodra decoder (attention with a sink, attention in
-blocks beside retention, wkv recurrences, dense GELU layers) beside the
-Llama-family decoder at equal width, depth, head count and feed-forward width,
+blocks beside retention, wkv recurrences, dense GELU layers) and the Nibelix
+decoder (lightning recurrences, differential attention over a window, dense and
+routed feed-forwards) beside the Llama-family decoder at equal width, depth, head count and feed-forward width,
 with random weights: one prompt of
 ``--prefill-tokens`` tokens and decode steps at ``--batch`` and ``--context``,
 for each of the size pairs in ``DESIGN_SIZES`` (or the one named by
@@ -146,6 +147,28 @@ def nikodra_config(z):
     layers = [NikodraLayer(kinds[i % 4][0], dict(kinds[i % 4][1]), dict(mlp)) for i in range(z["layers"])]
     return NikodraConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, residual_mult=0.5,
                          bigram={"buckets": 65521, "mul_prev": 1000003, "mul_cur": 31}, layers=layers)
+
+
+def nibelix_config(z):
+    """Nibelix at one of the size pairs: layers repeat lightning + dense, attention + routed, lightning + routed,
+    attention + dense.  Lightning states are 64 x head_dim (the Nikodra side's retention has the same); the two maps
+    of a differential head have head_dim / 2 features each, so a key row is as wide as the other sides' keys, over a
+    window of 1,024 positions; 14 experts and 2 identity outputs in 4 groups of which 2 are kept, 2 picks a token,
+    experts and the shared expert a quarter of the dense feed-forward's width."""
+    from exl3_server_b200.config.nibelix import NibelixConfig, NibelixLayer
+    hd = z["head_dim"]
+    lightning = {"heads": z["heads"], "dim": 64, "vdim": hd,
+                 "decay": [1.0 - 2.0 ** (-4.0 - 6.0 * i / z["heads"]) for i in range(z["heads"])]}
+    att = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": hd // 2, "vdim": hd, "scale": (hd // 2) ** -0.5,
+           "diff": 0.35, "mask": {"size": 1024}, "rot": {"base": 500000.0, "dims": hd // 2}}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4}, "shared": {"ff": z["ff"] // 4},
+           "router": {"experts": 14, "identity": 2, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}}}
+    kinds = [("lightning", lightning, dense), ("attention", att, moe), ("lightning", lightning, moe),
+             ("attention", att, dense)]
+    layers = [NibelixLayer(kinds[i % 4][0], dict(kinds[i % 4][1]), dict(kinds[i % 4][2])) for i in range(z["layers"])]
+    return NibelixConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, residual_mult=0.5, logit_softcap=30.0,
+                         layers=layers)
 
 
 def design_configs(name: str):
@@ -373,7 +396,7 @@ class Rig:
 
 
 def designs(args) -> int:
-    """``--only designs``: prefill and decode throughput of the Rigitar and Nikodra decoders beside the Llama-family
+    """``--only designs``: prefill and decode throughput of the Rigitar, Nikodra and Nibelix decoders beside the Llama-family
     decoder of equal sizes; one JSON line."""
     import torch
     torch.cuda.set_device(0)
@@ -387,7 +410,8 @@ def designs(args) -> int:
     for name in ([args.design_sizes] if args.design_sizes else sorted(DESIGN_SIZES)):
         rig_cfg, llama_cfg = design_configs(name)
         rec = {}
-        for arch, cfg in (("nikodra", nikodra_config(DESIGN_SIZES[name])), ("rigitar", rig_cfg), ("llama", llama_cfg)):
+        for arch, cfg in (("nibelix", nibelix_config(DESIGN_SIZES[name])), ("nikodra", nikodra_config(DESIGN_SIZES[name])),
+                          ("rigitar", rig_cfg), ("llama", llama_cfg)):
             if args.design_arch not in ("both", arch):
                 continue
             rig = Rig.of_config(f"{name}/{arch}", cfg, room, B + 1)
@@ -426,7 +450,7 @@ def main() -> int:
                     help="run one part only (for profiling small cases); prints a short JSON line")
     ap.add_argument("--design-sizes", choices=sorted(DESIGN_SIZES), default=None,
                     help="with --only designs: one size pair instead of all")
-    ap.add_argument("--design-arch", choices=["both", "nikodra", "rigitar", "llama"], default="both",
+    ap.add_argument("--design-arch", choices=["both", "nibelix", "nikodra", "rigitar", "llama"], default="both",
                     help="with --only designs: one of the designs only (both: all of them)")
     ap.add_argument("--design-part", choices=["both", "prefill", "decode"], default="both",
                     help="with --only designs: one of the two measurements only")

@@ -303,12 +303,26 @@ int exl3_tanh_norm_add(float* h, const void* a, int a_dtype, const void* b, int 
 // exl3_moe_gemm: out[p] = act(W[e(p)] A[p / a_div]) for the planned pairs, W [n_experts, N, K]; act 0 none, 1 gelu
 // (exact), 2 gelu by the tanh formula, 3 silu.  exl3_moe_combine: the weighted sum, float32 [T, H]; picks from
 // n_experts on stand for the input x itself; shared (any type) is added times gate (null: as it is).
+// exl3_moe_gemv: the same product for plans of tiles of at most exl3_moe_gemv_rows() rows (decode), bfloat16 A and W.
+// exl3_moe_gather + exl3_moe_gemm_tc (moe_tc.cu): rows of x in the plan's order, and the product on tcgen05 tensor
+// cores for plans of tiles of at most exl3_moe_tc_rows() rows; out bfloat16 in the plan's order or float32 at the
+// pairs' own places.  plan[1] holds the number of planned pairs.
 int exl3_moe_tile_rows();
-int exl3_moe_max_tiles(int P, int n_experts);
+int exl3_moe_gemv_rows();
+int exl3_moe_tc_rows();
+int exl3_moe_tc_status();
+int exl3_moe_tc_supported(int N, int K);
+int exl3_moe_max_tiles(int P, int n_experts, int tile_rows);
+int exl3_moe_gemv(const void* A, int64_t lda, int a_div, const void* W, const int* order, const int* plan, void* out,
+                  int out_dtype, int P, int n_experts, int N, int K, int act, cudaStream_t stream);
+int exl3_moe_gather(const void* x, int64_t ldx, int top, const int* order, const int* plan, void* xs, int P, int K,
+                    cudaStream_t stream);
+int exl3_moe_gemm_tc(const void* A, const void* W, const int* order, const int* plan, void* out, int out_dtype, int P,
+                     int n_experts, int N, int K, int act, cudaStream_t stream);
 int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const float* wr, const float* corr, int T, int W, int E,
                    int extra, int groups, int keep, int top, float scale, int score_kind, int* idx, float* wt,
                    float* gate_out, cudaStream_t stream);
-int exl3_moe_plan(const int* idx, int P, int n_experts, int* order, int* plan, cudaStream_t stream);
+int exl3_moe_plan(const int* idx, int P, int n_experts, int tile_rows, int* order, int* plan, cudaStream_t stream);
 int exl3_moe_gemm(const void* A, int a_dtype, int64_t lda, int a_div, const void* W, int w_dtype, const int* order,
                   const int* plan, void* out, int out_dtype, int P, int n_experts, int N, int K, int act,
                   cudaStream_t stream);

@@ -482,6 +482,51 @@ head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, c
   }
 }
 
+// The same for wide heads (all heads normed together make one of heads * dv values): a block per (token, head), the
+// head's values kept in registers between the sum of squares and the output (up to HN_WIDE_PER values a thread; what is
+// beyond is read again).
+constexpr int HN_WIDE_THREADS = 256, HN_WIDE_PER = 8;
+
+__global__ void __launch_bounds__(HN_WIDE_THREADS)
+head_norm_gate_wide_kernel(const float* o, const void* __restrict__ w, int w_dtype, const void* gate, int gate_dtype,
+                           int64_t gate_ld, int gate_kind, float eps, void* out, int out_dtype, int heads, int dv) {
+  __shared__ float red[32];
+  pdl_wait();
+  pdl_trigger();
+  const int item = blockIdx.x;
+  const int t = item / heads, hd = item - t * heads;
+  const float* src = o + (int64_t)item * dv;
+  float x[HN_WIDE_PER];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < HN_WIDE_PER; ++i) {
+    const int e = threadIdx.x + i * HN_WIDE_THREADS;
+    x[i] = e < dv ? __ldcg(src + e) : 0.0f;
+    ss = fmaf(x[i], x[i], ss);
+  }
+  for (int e = threadIdx.x + HN_WIDE_PER * HN_WIDE_THREADS; e < dv; e += HN_WIDE_THREADS) {
+    const float v = __ldcg(src + e);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
+  auto emit = [&](int e, float v) {
+    v *= inv;
+    if (w) v *= ls_load(w, w_dtype, (int64_t)hd * dv + e);
+    if (gate) {
+      const float g = ls_load_act(gate, gate_dtype, (int64_t)t * gate_ld + (int64_t)hd * dv + e);
+      v *= (gate_kind == 1 ? 1.0f : g) / (1.0f + expf(-g));
+    }
+    ls_store(out, out_dtype, (int64_t)item * dv + e, v);
+  };
+#pragma unroll
+  for (int i = 0; i < HN_WIDE_PER; ++i) {
+    const int e = threadIdx.x + i * HN_WIDE_THREADS;
+    if (e < dv) emit(e, x[i]);
+  }
+  for (int e = threadIdx.x + HN_WIDE_PER * HN_WIDE_THREADS; e < dv; e += HN_WIDE_THREADS) emit(e, __ldcg(src + e));
+}
+
 // The same with four values a lane (dv a multiple of 4, at most 128 a head: one piece a lane), float32 weight.
 template <typename TG, typename TO>
 __global__ void __launch_bounds__(128)
@@ -631,7 +676,10 @@ extern "C" int exl3_head_norm_gate(const float* o, const void* w, int w_dtype, c
                    (gate == nullptr || gate_ld % 4 == 0);
   const float* wf = static_cast<const float*>(w);
   const dim3 grid(ceil_div(items, 4)), threads(128);
-  if (vec && gate_dtype == DT_BF16 && out_dtype == DT_BF16)
+  if (dv > 256)
+    launch_pdl(head_norm_gate_wide_kernel, dim3(items), dim3(HN_WIDE_THREADS), 0, stream, o, w, w_dtype, gate, gate_dtype,
+               gate_ld, gate_kind, eps, out, out_dtype, heads, dv);
+  else if (vec && gate_dtype == DT_BF16 && out_dtype == DT_BF16)
     launch_pdl(head_norm_gate_vec_kernel<__nv_bfloat16, __nv_bfloat16>, grid, threads, 0, stream, o, wf,
                static_cast<const __nv_bfloat16*>(gate), gate_ld, gate_kind, eps, static_cast<__nv_bfloat16*>(out), items, heads, dv);
   else if (vec && gate_dtype == DT_F32 && out_dtype == DT_BF16)

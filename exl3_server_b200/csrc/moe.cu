@@ -7,7 +7,7 @@
 //            weight s * scale (no renormalisation).  One more row of Wr may follow the router's: its sigmoid is a
 //            gate per token (for a shared expert) that the same kernel leaves beside the picks.
 //   plan     the pairs (token, pick) whose pick is an expert with weights, ordered by expert and cut into tiles of
-//            at most MOE_TM rows of one expert; everything stays on the device (no count reaches the host), so the
+//            at most a given number of rows of one expert; everything stays on the device (no count reaches the host), so the
 //            step can be part of a recorded graph.
 //   experts  mid[p] = act(W_up[e] x[token(p)]),  y[p] = W_down[e] mid[p], a block per (tile, 64 output features);
 //            a row's sum walks K in order with one float32 accumulator, so it does not depend on the row's tile mates.
@@ -21,6 +21,7 @@
 namespace exl3 {
 
 constexpr int RT_TOK = 4;        // tokens a block of the router takes (one a warp for the choice)
+constexpr int RT_WARPS = 16;     // warps of a block: router outputs go round over them
 constexpr int RT_KC = 512;       // columns of x staged at a time
 constexpr int MOE_TM = 32;       // rows of a tile
 constexpr int MOE_TN = 64;       // output features of a block
@@ -45,7 +46,7 @@ __device__ inline void warp_argmax(float& v, int& i) {
 }
 
 template <typename TX>
-__global__ void __launch_bounds__(RT_TOK * 32)
+__global__ void __launch_bounds__(RT_WARPS * 32)
 moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const float* __restrict__ corr, int T, int W,
                  int E, int S, int groups, int keep, int top, float scale, int score_kind, int* idx, float* wt,
                  float* gate_out) {
@@ -69,15 +70,19 @@ moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const f
       xs[i] = (t0 + tok < T && col < kc) ? moe_ld(x + (int64_t)(t0 + tok) * ldx + k0 + col) : 0.0f;
     }
     __syncthreads();
-    for (int e = warp; e < R; e += RT_TOK) {
+    for (int e = warp; e < R; e += RT_WARPS) {
       const float* wrow = wr + (int64_t)e * W + k0;
       float part[RT_TOK];
 #pragma unroll
       for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = 0.0f;
-      for (int col = lane; col < kc; col += 32) {
-        const float w = wrow[col];
+      // a fixed number of rounds, so that the row's loads are all under way before the first is used
+      float wv[RT_KC / 32];
 #pragma unroll
-        for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = fmaf(w, xs[tok * RT_KC + col], part[tok]);
+      for (int i = 0; i < RT_KC / 32; ++i) wv[i] = lane + 32 * i < kc ? wrow[lane + 32 * i] : 0.0f;
+#pragma unroll
+      for (int i = 0; i < RT_KC / 32; ++i) {
+#pragma unroll
+        for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = fmaf(wv[i], xs[tok * RT_KC + lane + 32 * i], part[tok]);
       }
 #pragma unroll
       for (int tok = 0; tok < RT_TOK; ++tok) {
@@ -88,7 +93,7 @@ moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const f
   }
   __syncthreads();
   const int t = t0 + warp;                         // this warp's token
-  if (t >= T) return;
+  if (warp >= RT_TOK || t >= T) return;
   float* zt = z + warp * R;
   float* ct = c + warp * E;
   float* gst = gs + warp * groups;
@@ -160,9 +165,10 @@ moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const f
   }
 }
 
-// One block.  plan[0]: number of tiles; then per tile (expert, first place in `order`, rows), from plan[4] on.
+// One block.  plan[0]: number of tiles; plan[1]: planned pairs (places of `order` in use); then per tile (expert,
+// first place in `order`, rows), from plan[4] on.  Tiles hold at most tile_rows rows.
 __global__ void __launch_bounds__(1024)
-moe_plan_kernel(const int* idx, int P, int n_experts, int* order, int* plan) {
+moe_plan_kernel(const int* idx, int P, int n_experts, int tile_rows, int* order, int* plan) {
   extern __shared__ int ps[];                      // counts, offsets, cursors
   int* counts = ps;
   int* offs = ps + n_experts;
@@ -180,15 +186,16 @@ moe_plan_kernel(const int* idx, int P, int n_experts, int* order, int* plan) {
     int off = 0, nt = 0;
     for (int e = 0; e < n_experts; ++e) {
       offs[e] = off;
-      for (int r = 0; r < counts[e]; r += MOE_TM) {
+      for (int r = 0; r < counts[e]; r += tile_rows) {
         plan[4 + 3 * nt] = e;
         plan[5 + 3 * nt] = off + r;
-        plan[6 + 3 * nt] = min(MOE_TM, counts[e] - r);
+        plan[6 + 3 * nt] = min(tile_rows, counts[e] - r);
         ++nt;
       }
       off += counts[e];
     }
     plan[0] = nt;
+    plan[1] = off;
   }
   __syncthreads();
   for (int p = threadIdx.x; p < P; p += blockDim.x) {
@@ -264,6 +271,84 @@ moe_gemm_kernel(const TA* A, int64_t lda, int a_div, const TW* __restrict__ Wt, 
   }
 }
 
+
+// ---- a few rows per expert (decode): the experts' matrices are read once, a warp per output feature ---------------
+//
+// out[p, n] = act(sum_k A[p / a_div, k] * W[e(p), n, k]) for tiles of at most MV_ROWS pairs: a warp takes MV_FEAT output
+// features, reads their rows of W in 16-byte pieces (all features' loads under way together) and keeps one float32
+// sum per (feature, pair); lanes' sums meet in a fixed order, so a pair's result does not depend on its tile mates.
+constexpr int MV_ROWS = 8, MV_FEAT = 4, MV_WARPS = 8;
+
+template <typename TO>
+__global__ void __launch_bounds__(MV_WARPS * 32)
+moe_gemv_kernel(const __nv_bfloat16* A, int64_t lda, int a_div, const __nv_bfloat16* __restrict__ Wt, const int* order,
+                const int* plan, TO* out, int N, int K, int act) {
+  __shared__ int rows[MV_ROWS];
+  pdl_wait();
+  pdl_trigger();
+  const int tile = blockIdx.x;
+  if (tile >= __ldcg(plan)) return;
+  const int e = __ldcg(plan + 4 + 3 * tile), start = __ldcg(plan + 5 + 3 * tile), nrows = __ldcg(plan + 6 + 3 * tile);
+  if (threadIdx.x < MV_ROWS) rows[threadIdx.x] = threadIdx.x < nrows ? __ldcg(order + start + threadIdx.x) : -1;
+  __syncthreads();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n0 = (blockIdx.y * MV_WARPS + warp) * MV_FEAT;
+  if (n0 >= N) return;
+  const __nv_bfloat16* Wexp = Wt + (int64_t)e * N * K;
+  float acc[MV_FEAT][MV_ROWS];
+#pragma unroll
+  for (int f = 0; f < MV_FEAT; ++f)
+#pragma unroll
+    for (int r = 0; r < MV_ROWS; ++r) acc[f][r] = 0.0f;
+  for (int k = lane * 8; k < K; k += 256) {
+    uint4 wv[MV_FEAT];
+#pragma unroll
+    for (int f = 0; f < MV_FEAT; ++f) {
+      const int n = min(n0 + f, N - 1);
+      wv[f] = __ldg(reinterpret_cast<const uint4*>(Wexp + (int64_t)n * K + k));
+    }
+#pragma unroll
+    for (int r = 0; r < MV_ROWS; ++r) {
+      const int p = rows[r];
+      if (p < 0) continue;
+      const uint4 xv = __ldcg(reinterpret_cast<const uint4*>(A + (int64_t)(p / a_div) * lda + k));
+      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+#pragma unroll
+      for (int f = 0; f < MV_FEAT; ++f) {
+        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[f]);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 a = __bfloat1622float2(xp[j]), b = __bfloat1622float2(wp[j]);
+          acc[f][r] = fmaf(a.x, b.x, acc[f][r]);
+          acc[f][r] = fmaf(a.y, b.y, acc[f][r]);
+        }
+      }
+    }
+  }
+#pragma unroll
+  for (int f = 0; f < MV_FEAT; ++f)
+#pragma unroll
+    for (int r = 0; r < MV_ROWS; ++r) {
+      const float v = warp_sum(acc[f][r]);
+      const int p = rows[r];
+      if (lane == 0 && p >= 0 && n0 + f < N) moe_st(out + (int64_t)p * N + n0 + f, moe_act(v, act));
+    }
+}
+
+// xs[i] = x[order[i] / top] for the planned pairs, in the plan's order (rows of K bfloat16, 16 bytes a thread).
+__global__ void __launch_bounds__(256)
+moe_gather_kernel(const __nv_bfloat16* x, int64_t ldx, int top, const int* order, const int* plan, __nv_bfloat16* xs,
+                  int K) {
+  pdl_wait();
+  pdl_trigger();
+  const int i = blockIdx.x;
+  if (i >= __ldcg(plan + 1)) return;
+  const int p = __ldcg(order + i);
+  const uint4* src = reinterpret_cast<const uint4*>(x + (int64_t)(p / top) * ldx);
+  uint4* dst = reinterpret_cast<uint4*>(xs + (int64_t)i * K);
+  for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = __ldcg(src + c);
+}
+
 template <typename TX>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* y, const int* idx, const float* wt, const TX* x, int64_t ldx, const void* shared,
@@ -316,7 +401,7 @@ extern "C" int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const flo
                         : cudaFuncSetAttribute(kernel_h, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_error("moe_route: shared memory refused: %s", cudaGetErrorString(e)); return (int)e; }
   }
-  const dim3 grid(ceil_div(T, RT_TOK)), threads(RT_TOK * 32);
+  const dim3 grid(ceil_div(T, RT_TOK)), threads(RT_WARPS * 32);
   if (x_dtype == DT_F32)
     launch_pdl(kernel, grid, threads, smem, stream, static_cast<const float*>(x), ldx, wr, corr, T, W, E, extra, groups,
                keep, top, scale, score_kind, idx, wt, gate_out);
@@ -327,21 +412,24 @@ extern "C" int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const flo
   return launch_status("moe_route");
 }
 
-extern "C" int exl3_moe_plan(const int* idx, int P, int n_experts, int* order, int* plan, cudaStream_t stream) {
+extern "C" int exl3_moe_plan(const int* idx, int P, int n_experts, int tile_rows, int* order, int* plan,
+                             cudaStream_t stream) {
   if (P == 0) return 0;
-  if (P < 0 || n_experts < 1 || n_experts > 4096) { set_error("moe_plan: bad sizes"); return ERR_BAD_ARGUMENT; }
-  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), (size_t)3 * n_experts * sizeof(int), stream, idx, P, n_experts, order,
-             plan);
+  if (P < 0 || n_experts < 1 || n_experts > 4096 || tile_rows < 1) { set_error("moe_plan: bad sizes"); return ERR_BAD_ARGUMENT; }
+  launch_pdl(moe_plan_kernel, dim3(1), dim3(1024), (size_t)3 * n_experts * sizeof(int), stream, idx, P, n_experts,
+             tile_rows, order, plan);
   return launch_status("moe_plan");
 }
 
-// The most tiles a step of P pairs over n_experts experts can have.
-extern "C" int exl3_moe_max_tiles(int P, int n_experts) { return min(P, P / MOE_TM + n_experts); }
+// The most tiles of at most tile_rows rows that a step of P pairs over n_experts experts can have.
+extern "C" int exl3_moe_max_tiles(int P, int n_experts, int tile_rows) {
+  return tile_rows < 1 ? 0 : min(P, P / tile_rows + n_experts);
+}
 
 template <typename TA, typename TW, typename TO>
 static int moe_gemm_launch(const void* A, int64_t lda, int a_div, const void* W, const int* order, const int* plan,
                            void* out, int P, int n_experts, int N, int K, int act, cudaStream_t stream) {
-  const dim3 grid(exl3_moe_max_tiles(P, n_experts), ceil_div(N, MOE_TN));
+  const dim3 grid(exl3_moe_max_tiles(P, n_experts, MOE_TM), ceil_div(N, MOE_TN));
   launch_pdl(moe_gemm_kernel<TA, TW, TO>, grid, dim3(256), 0, stream, static_cast<const TA*>(A), lda, a_div,
              static_cast<const TW*>(W), order, plan, static_cast<TO*>(out), N, K, act);
   return launch_status("moe_gemm");
@@ -367,6 +455,45 @@ extern "C" int exl3_moe_gemm(const void* A, int a_dtype, int64_t lda, int a_div,
 #undef EXL3_MOE
   set_error("moe_gemm: unsupported element types %d x %d -> %d", a_dtype, w_dtype, out_dtype);
   return ERR_UNSUPPORTED;
+}
+
+extern "C" int exl3_moe_gemv_rows() { return MV_ROWS; }
+
+// The same product as exl3_moe_gemm for a plan of tiles of at most exl3_moe_gemv_rows() rows; bfloat16 A and W with K a
+// multiple of 8 and 16-byte aligned rows; out bfloat16 or float32.
+extern "C" int exl3_moe_gemv(const void* A, int64_t lda, int a_div, const void* W, const int* order, const int* plan,
+                             void* out, int out_dtype, int P, int n_experts, int N, int K, int act, cudaStream_t stream) {
+  if (P == 0) return 0;
+  if (P < 0 || n_experts < 1 || N < 1 || K < 8 || K % 8 != 0 || lda % 8 != 0 || a_div < 1 || act < 0 || act > 3 ||
+      !aligned16(A) || !aligned16(W)) {
+    set_error("moe_gemv: bad sizes pairs=%d experts=%d N=%d K=%d (K and the row pitch multiples of 8, 16-byte aligned)", P,
+              n_experts, N, K);
+    return ERR_BAD_ARGUMENT;
+  }
+  const dim3 grid(exl3_moe_max_tiles(P, n_experts, MV_ROWS), ceil_div(N, MV_WARPS * MV_FEAT));
+  if (grid.y > 65535) { set_error("moe_gemv: grid too large"); return ERR_UNSUPPORTED; }
+  const __nv_bfloat16* a = static_cast<const __nv_bfloat16*>(A);
+  const __nv_bfloat16* w = static_cast<const __nv_bfloat16*>(W);
+  if (out_dtype == DT_BF16)
+    launch_pdl(moe_gemv_kernel<__nv_bfloat16>, grid, dim3(MV_WARPS * 32), 0, stream, a, lda, a_div, w, order, plan,
+               static_cast<__nv_bfloat16*>(out), N, K, act);
+  else if (out_dtype == DT_F32)
+    launch_pdl(moe_gemv_kernel<float>, grid, dim3(MV_WARPS * 32), 0, stream, a, lda, a_div, w, order, plan,
+               static_cast<float*>(out), N, K, act);
+  else { set_error("moe_gemv: unsupported output type %d", out_dtype); return ERR_UNSUPPORTED; }
+  return launch_status("moe_gemv");
+}
+
+extern "C" int exl3_moe_gather(const void* x, int64_t ldx, int top, const int* order, const int* plan, void* xs, int P,
+                               int K, cudaStream_t stream) {
+  if (P == 0) return 0;
+  if (P < 0 || top < 1 || K < 8 || K % 8 != 0 || ldx % 8 != 0 || !aligned16(x) || !aligned16(xs)) {
+    set_error("moe_gather: bad sizes pairs=%d K=%d", P, K);
+    return ERR_BAD_ARGUMENT;
+  }
+  launch_pdl(moe_gather_kernel, dim3(P), dim3(256), 0, stream, static_cast<const __nv_bfloat16*>(x), ldx, top, order, plan,
+             static_cast<__nv_bfloat16*>(xs), K);
+  return launch_status("moe_gather");
 }
 
 extern "C" int exl3_moe_combine(const float* y, const int* idx, const float* wt, const void* x, int x_dtype, int64_t ldx,

@@ -994,13 +994,13 @@ def attn_decode(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool: t
 
 def check_status() -> None:
     """Raises if a kernel with bounded waits (the tcgen05 GEMMs and attention, the TMA decode attention) gave up
-    on one since the last call: its results are then not to be trusted.  Reads four flags from the device, so
+    on one since the last call: its results are then not to be trusted.  Reads their flags from the device, so
     it waits for the work launched so far; call it where the host waits anyway."""
     gave_up = [name for name, fn in (("gemm_tc", gemm_tc_status), ("gemm_skinny", gemm_skinny_status),
                                      ("gemm_pair", gemm_pair_status),
                                      ("attn_prefill_tc", attn_prefill_tc_status),
                                      ("attn_decode", attn_decode_status),
-                                     ("attn_latent", attn_latent_status)) if fn()]
+                                     ("attn_latent", attn_latent_status), ("moe_gemm_tc", moe_tc_status)) if fn()]
     if gave_up:
         raise KernelLibraryError("a bounded wait ran out in " + ", ".join(gave_up) +
                                  ": a copy or a tensor-core product did not complete in time")
@@ -1120,8 +1120,24 @@ MOE_ACTIVATIONS = {"none": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3}
 MOE_SCORES = {"softmax": 0, "sigmoid": 1}
 
 
-def moe_max_tiles(pairs: int, n_experts: int) -> int:
-    return int(library().exl3_moe_max_tiles(_c_int(pairs), _c_int(n_experts)))
+def moe_tile_rows(kind: str = "tile") -> int:
+    """Rows of a plan's tiles for the CUDA-core product (``"tile"``), the few-row product (``"few"``) and the
+    tensor-core product (``"tc"``)."""
+    lib = library()
+    return int({"tile": lib.exl3_moe_tile_rows, "few": lib.exl3_moe_gemv_rows, "tc": lib.exl3_moe_tc_rows}[kind]())
+
+
+def moe_max_tiles(pairs: int, n_experts: int, tile_rows: int) -> int:
+    return int(library().exl3_moe_max_tiles(_c_int(pairs), _c_int(n_experts), _c_int(tile_rows)))
+
+
+def moe_tc_supported(dtype: torch.dtype, n: int, k: int) -> bool:
+    return dtype == torch.bfloat16 and bool(library().exl3_moe_tc_supported(_c_int(n), _c_int(k)))
+
+
+def moe_tc_status() -> int:
+    """0, or the code the tensor-core experts' product left when a bounded wait ran out (cleared by this call)."""
+    return int(library().exl3_moe_tc_status())
 
 
 def moe_route(x: torch.Tensor, wr: torch.Tensor, corr: torch.Tensor, outputs: int, extra: int, groups: int, keep: int,
@@ -1146,16 +1162,67 @@ def moe_route(x: torch.Tensor, wr: torch.Tensor, corr: torch.Tensor, outputs: in
     return idx, wt, gate
 
 
-def moe_plan(idx: torch.Tensor, n_experts: int):
-    """Orders a step's (token, pick) pairs by expert and cuts them into tiles, on the device.  Returns ``(order int32
-    [pairs], plan int32)`` for ``moe_gemm``; picks outside ``0 .. n_experts - 1`` (identity outputs) are left out."""
+def moe_plan(idx: torch.Tensor, n_experts: int, tile_rows: int = 0):
+    """Orders a step's (token, pick) pairs by expert and cuts them into tiles of at most ``tile_rows`` rows (0: the
+    CUDA-core product's), on the device.  Returns ``(order int32 [pairs], plan int32)`` for the experts' products;
+    picks outside ``0 .. n_experts - 1`` (identity outputs) are left out."""
     _contig(idx, "idx")
     P = idx.numel()
+    tile_rows = tile_rows or moe_tile_rows()
     order = torch.empty((P,), dtype=torch.int32, device=idx.device)
-    plan = torch.empty((4 + 3 * max(1, moe_max_tiles(P, n_experts)),), dtype=torch.int32, device=idx.device)
-    _check(library().exl3_moe_plan(_ptr(idx), _c_int(P), _c_int(n_experts), _ptr(order), _ptr(plan), _stream()),
-           "moe_plan")
+    plan = torch.empty((4 + 3 * max(1, moe_max_tiles(P, n_experts, tile_rows)),), dtype=torch.int32, device=idx.device)
+    _check(library().exl3_moe_plan(_ptr(idx), _c_int(P), _c_int(n_experts), _c_int(tile_rows), _ptr(order), _ptr(plan),
+                                   _stream()), "moe_plan")
     return order, plan
+
+
+def moe_gemv(a: torch.Tensor, a_div: int, w: torch.Tensor, order: torch.Tensor, plan: torch.Tensor,
+             out_dtype: torch.dtype, act: str = "none") -> torch.Tensor:
+    """``moe_gemm`` for a plan of tiles of at most ``moe_tile_rows("few")`` rows (decode): bfloat16 ``a`` and ``w``, inputs
+    a multiple of 8 wide; every expert's matrix is read once, a warp per output feature."""
+    E, N, Kd = w.shape
+    _contig(w, "w")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.stride(1) != 1 or a.shape[1] != Kd:
+        raise KernelLibraryError("moe_gemv: a and w must be bfloat16, rows of a dense and as wide as the experts' inputs")
+    P = order.numel()
+    out = torch.empty((P, N), dtype=out_dtype, device=a.device)
+    _check(library().exl3_moe_gemv(
+        _ptr(a), _c_int64(a.stride(0)), _c_int(a_div), _ptr(w), _ptr(order), _ptr(plan), _ptr(out),
+        _c_int(dtype_code(out_dtype)), _c_int(P), _c_int(E), _c_int(N), _c_int(Kd), _c_int(MOE_ACTIVATIONS[act]),
+        _stream()), "moe_gemv")
+    return out
+
+
+def moe_gather(x: torch.Tensor, top: int, order: torch.Tensor, plan: torch.Tensor) -> torch.Tensor:
+    """Rows of ``x [T, K]`` (bfloat16) in the plan's order: row i is ``x[order[i] // top]`` for the planned pairs (the
+    rest of the ``[pairs, K]`` result is not written)."""
+    if x.dtype != torch.bfloat16 or x.stride(1) != 1:
+        raise KernelLibraryError("moe_gather: x must be bfloat16 with dense rows")
+    P = order.numel()
+    xs = torch.empty((P, x.shape[1]), dtype=x.dtype, device=x.device)
+    _check(library().exl3_moe_gather(_ptr(x), _c_int64(x.stride(0)), _c_int(top), _ptr(order), _ptr(plan), _ptr(xs),
+                                     _c_int(P), _c_int(x.shape[1]), _stream()), "moe_gather")
+    return xs
+
+
+def moe_gemm_tc(a: torch.Tensor, w: torch.Tensor, order: torch.Tensor, plan: torch.Tensor, out_dtype: torch.dtype,
+                act: str = "none") -> torch.Tensor:
+    """The experts' product on tcgen05 tensor cores (see moe_tc.cu) for a plan of tiles of at most
+    ``moe_tile_rows("tc")`` rows: ``a [pairs, K]`` bfloat16 in the plan's order, ``w [experts, N, K]`` bfloat16.  A bfloat16
+    result is in the plan's order too; a float32 one has every pair at its own place (``order[i]``)."""
+    E, N, Kd = w.shape
+    _contig(w, "w")
+    _contig(a, "a")
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.shape[1] != Kd:
+        raise KernelLibraryError("moe_gemm_tc: a and w must be bfloat16 and a as wide as the experts' inputs")
+    P = order.numel()
+    if a.shape[0] != P:
+        raise KernelLibraryError("moe_gemm_tc: a must have a row per pair")
+    out = torch.empty((P, N), dtype=out_dtype, device=a.device)
+    _check(library().exl3_moe_gemm_tc(
+        _ptr(a), _ptr(w), _ptr(order), _ptr(plan), _ptr(out), _c_int(dtype_code(out_dtype)), _c_int(P), _c_int(E),
+        _c_int(N), _c_int(Kd), _c_int(MOE_ACTIVATIONS[act]), _stream()), "moe_gemm_tc")
+    return out
 
 
 def moe_gemm(a: torch.Tensor, a_div: int, w: torch.Tensor, order: torch.Tensor, plan: torch.Tensor,

@@ -23,6 +23,10 @@ key row is the map's score (``kernels.maps_prep`` rotates, widens and writes the
 kernels then run ``2 * heads`` query heads over ``kv_heads`` key/value heads with the window as their parameter and
 leave float32 outputs; ``kernels.diff_combine`` subtracts, norms and gates in float32.  Scores, softmax, lambda, the
 subtraction and the norm are float32 in either element type.
+
+In bfloat16, a key row of 64 or 128 features with values no wider is the shape of the tensor-core attention kernels:
+the value row is then as wide as the key row, and the maps run through the same choice of kernels as the
+``attention`` mixer's heads (tcgen05 prompts, TMA decode), whose bfloat16 outputs ``diff_combine`` reads.
 """
 from __future__ import annotations
 
@@ -33,7 +37,7 @@ import torch
 
 from ..ops import kernels as K
 from ..weights.loader import TensorSpec
-from .attention import BUSY_ITEMS, SPLIT_KEYS
+from .attention import BUSY_ITEMS, SPLIT_KEYS, Attention
 from .base import BuildContext, KVRequest, StateRequest
 from .linear import Linear
 from .registry import position_class, register_mixer
@@ -44,6 +48,14 @@ MAPS = 2
 
 def pad8(n: int) -> int:
     return (n + 7) // 8 * 8
+
+
+class MapsAsHeads(Attention):
+    """The ``attention`` mixer's choice of kernels for queries that are already prepared: ``heads`` here are the
+    maps, all of the key row's width, over keys and values that are in the cache."""
+
+    def __init__(self, spec: MixerSpec, scale: float, ctx: BuildContext):
+        self.spec, self.scale, self.ctx = spec, scale, ctx
 
 
 class DifferentialAttention:
@@ -70,6 +82,12 @@ class DifferentialAttention:
         self.spec, self.ctx = spec, ctx
         self.H, self.G, self.d, self.dv = H, G, d, dv
         self.row, self.v_row = pad8(MAPS * d), pad8(dv)
+        self.as_heads: Optional[MapsAsHeads] = None
+        if ctx.dtype == torch.bfloat16 and self.row in (64, 128) and dv <= self.row:
+            self.v_row = self.row
+            self.as_heads = MapsAsHeads(
+                MixerSpec(kind="attention", width=spec.width, heads=H * MAPS, kv_heads=G, head_dim=self.row,
+                          window=int(spec.window)), 0.0, ctx)
         self.eps = float(p.get("norm_eps", 1e-6))
         self.lambda0 = float(p["lambda0"])
         self.window = int(spec.window)
@@ -91,6 +109,8 @@ class DifferentialAttention:
             raise ValueError("differential attention: only the half-split rotary layout")
         self.position = position_class(pos.kind)(pos, d, ctx)
         self.rot = int(self.position.spec.dims)
+        if self.as_heads is not None:
+            self.as_heads.scale = self.scale
 
     def cache_request(self) -> Optional[KVRequest]:
         return KVRequest(self.G, self.row, self.window, self.v_row if self.v_row != self.row else 0)
@@ -117,9 +137,14 @@ class DifferentialAttention:
         return self.o(y, out_dtype=self.o.wide_dtype(T))
 
     def _attend(self, q: torch.Tensor, batch, kv) -> torch.Tensor:
-        """Both maps of every head as ``2 * heads`` query heads: float32 ``[T, heads * 2 * value row]``."""
+        """Both maps of every head as ``2 * heads`` query heads: ``[T, heads * 2 * value row]``, float32 from the
+        CUDA-core kernel, bfloat16 from the tensor-core ones."""
         T = q.shape[0]
         nh = self.H * MAPS
+        if self.as_heads is not None:
+            out = torch.empty((T, nh * self.v_row), dtype=q.dtype, device=q.device)
+            self.as_heads.attend(q, out, batch, kv)
+            return out
         out = torch.empty((T, nh * self.v_row), dtype=torch.float32, device=q.device)
         split = max(SPLIT_KEYS, kv.page_size)
         if split % kv.page_size:

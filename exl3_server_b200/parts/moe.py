@@ -19,7 +19,10 @@ How it runs (``csrc/moe.cu``): the router kernel also computes the shared expert
 of the router's float32 matrix); a one-block kernel orders the step's (token, pick) pairs by expert into tiles, on the
 device, so a step is the same list of launches whatever the router chose (it can be part of a recorded graph); the
 experts' weights are stacked ``[experts, out, in]`` and both projections are grouped products over the tiles; the
-last kernel sums picks, identity picks and the gated shared expert in float32.
+last kernel sums picks, identity picks and the gated shared expert in float32.  Which product runs depends on the
+step only through its number of pairs: in bfloat16, few pairs (decode) take the kernel that reads each expert's
+matrix once with a warp per output feature, many pairs (prompts) are gathered into the plan's order and go through
+the tcgen05 grouped product; float32, and sizes those two do not take, use the CUDA-core tiles.
 """
 from __future__ import annotations
 
@@ -33,6 +36,10 @@ from .base import BuildContext
 from .ffn import DenseFeedForward
 from .registry import register_feed_forward
 from .spec import FeedForwardSpec
+
+
+FEW_PAIRS = 128       # up to here the few-row product; from MANY_PAIRS on the tensor cores
+MANY_PAIRS = 512
 
 
 class RoutedFeedForward:
@@ -89,11 +96,28 @@ class RoutedFeedForward:
                                     self.groups, self.keep, self.top, self.scale, self.score)
         y = None
         if self.E:
-            order, plan = K.moe_plan(idx, self.E)
-            mid = K.moe_gemm(x, self.top, self.w_up, order, plan, self.dtype, act=self.act)
-            y = K.moe_gemm(mid, 1, self.w_down, order, plan, torch.float32)
+            y = self._experts(x, idx)
         s = self.shared.forward(x, batch) if self.shared is not None else None
         return K.moe_combine(y, idx, wt, x, s, gate, self.E)
+
+    def _experts(self, x: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+        """float32 ``[pairs, width]``: every planned pair's expert output at the pair's own place."""
+        pairs = idx.numel()
+        width, inner = self.w_up.shape[2], self.w_up.shape[1]
+        vec = self.dtype == torch.bfloat16 and x.dtype == torch.bfloat16 and width % 8 == 0 and inner % 8 == 0 and \
+            x.stride(0) % 8 == 0
+        if vec and pairs >= MANY_PAIRS and K.moe_tc_supported(self.dtype, inner, width):
+            order, plan = K.moe_plan(idx, self.E, K.moe_tile_rows("tc"))
+            xs = K.moe_gather(x, self.top, order, plan)
+            mid = K.moe_gemm_tc(xs, self.w_up, order, plan, self.dtype, act=self.act)
+            return K.moe_gemm_tc(mid, self.w_down, order, plan, torch.float32)
+        if vec and pairs <= FEW_PAIRS:
+            order, plan = K.moe_plan(idx, self.E, K.moe_tile_rows("few"))
+            mid = K.moe_gemv(x, self.top, self.w_up, order, plan, self.dtype, act=self.act)
+            return K.moe_gemv(mid, 1, self.w_down, order, plan, torch.float32)
+        order, plan = K.moe_plan(idx, self.E)
+        mid = K.moe_gemm(x, self.top, self.w_up, order, plan, self.dtype, act=self.act)
+        return K.moe_gemm(mid, 1, self.w_down, order, plan, torch.float32)
 
     def weight_bytes(self) -> int:
         """Weight bytes a token's step reads at most: the router, the shared expert and ``top`` experts per token

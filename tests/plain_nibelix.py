@@ -78,15 +78,17 @@ def differential_attention(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, 
     q = (h @ w[p + "q"].T).view(T, H * 2, d)                     # head by head: [map 1, map 2]
     k = (h @ w[p + "k"].T).view(T, G * 2, d)
     v = (h @ w[p + "v"].T).view(T, G, dv)
-    q = rotate_half_split(q, m["rot"]["dims"], m["rot"]["base"])
-    k = rotate_half_split(k, m["rot"]["dims"], m["rot"]["base"])
+    if m.get("rot") is not None:
+        q = rotate_half_split(q, m["rot"]["dims"], m["rot"]["base"])
+        k = rotate_half_split(k, m["rot"]["dims"], m["rot"]["base"])
+    window = m["mask"]["size"] if m.get("mask") is not None else T      # no mask in the configuration: every key before
     lam = math.exp(float((w[p + "lq1"] * w[p + "lk1"]).sum())) - math.exp(float((w[p + "lq2"] * w[p + "lk2"]).sum())) + diff
     gate = torch.sigmoid(h @ w[p + "g"].T)                       # [T, H]
     outs = []
     for hd in range(H):
         g = hd // (H // G)
-        a1 = windowed_softmax_attention(q[:, 2 * hd], k[:, 2 * g], v[:, g], m["scale"], m["mask"]["size"])
-        a2 = windowed_softmax_attention(q[:, 2 * hd + 1], k[:, 2 * g + 1], v[:, g], m["scale"], m["mask"]["size"])
+        a1 = windowed_softmax_attention(q[:, 2 * hd], k[:, 2 * g], v[:, g], m["scale"], window)
+        a2 = windowed_softmax_attention(q[:, 2 * hd + 1], k[:, 2 * g + 1], v[:, g], m["scale"], window)
         o = unit_rms(a1 - lam * a2, eps) * (1.0 - diff)
         outs.append(o * gate[:, hd:hd + 1])
     if probe is not None:
@@ -121,9 +123,12 @@ def small_expert(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str) -> torch.T
     return gelu_erf(h @ w[p + "up"].T) @ w[p + "down"].T
 
 
-def route(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, r: dict) -> List[List[Tuple[int, float]]]:
+def route(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, r: dict,
+          margins: Optional[list] = None) -> List[List[Tuple[int, float]]]:
     """Per token the chosen experts and their weights.  Router outputs number ``experts + identity``; the choice is
-    by score plus correction among the experts of the best groups, the weight is the score alone times a constant."""
+    by score plus correction among the experts of the best groups, the weight is the score alone times a constant.
+    ``margins`` gets, per token, how close the choice was: the smallest gap between something chosen and something
+    left out (groups and experts)."""
     n = r["experts"] + r["identity"]
     s = torch.softmax(h @ w[p + "router"].T, dim=-1)
     choice = s + w[p + "correction"]
@@ -131,17 +136,26 @@ def route(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, r: dict) -> List[
     out = []
     for t in range(h.shape[0]):
         c = choice[t]
-        best = sorted(range(r["groups"]["count"]), key=lambda g: -float(c[g * per:(g + 1) * per].max()))[:r["groups"]["keep"]]
-        open_ = [e for e in range(n) if e // per in best]
-        chosen = sorted(open_, key=lambda e: -float(c[e]))[:r["top"]]
+        by_group = sorted(range(r["groups"]["count"]), key=lambda g: -float(c[g * per:(g + 1) * per].max()))
+        best = by_group[:r["groups"]["keep"]]
+        open_ = sorted((e for e in range(n) if e // per in best), key=lambda e: -float(c[e]))
+        chosen = open_[:r["top"]]
+        if margins is not None:
+            gap = float("inf")
+            if len(by_group) > len(best):
+                gap = float(c[best[-1] * per:(best[-1] + 1) * per].max() - c[by_group[len(best)] * per:(by_group[len(best)] + 1) * per].max())
+            if len(open_) > len(chosen):
+                gap = min(gap, float(c[chosen[-1]] - c[open_[len(chosen)]]))
+            margins.append(gap)
         out.append([(e, float(s[t, e]) * r["scale"]) for e in chosen])
     return out
 
 
-def mixture_of_experts(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict) -> torch.Tensor:
+def mixture_of_experts(h: torch.Tensor, w: Dict[str, torch.Tensor], p: str, mlp: dict,
+                       margins: Optional[list] = None) -> torch.Tensor:
     r = mlp["router"]
     y = torch.zeros_like(h)
-    for t, picks in enumerate(route(h, w, p, r)):
+    for t, picks in enumerate(route(h, w, p, r, margins)):
         for e, weight in picks:
             if e >= r["experts"]:                                 # an identity expert: the input itself
                 y[t] += weight * h[t]
@@ -156,7 +170,8 @@ def soft_cap(z: torch.Tensor, cap: float) -> torch.Tensor:
     return cap * torch.tanh(z / cap)
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None) -> torch.Tensor:
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], layers_out: Optional[list] = None,
+            margins: Optional[list] = None) -> torch.Tensor:
     """Logits [T, vocab] (float64) of one whole sequence."""
     eps, m = cfg["norm"]["eps"], cfg["residual_mult"]
     x = w["embed"][torch.tensor(tokens, dtype=torch.long)]
@@ -173,13 +188,13 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], layers_out
             if layer["mlp"]["kind"] == "dense":
                 f = dense_feed_forward(h2, w, p + "mlp.")
             else:
-                f = mixture_of_experts(h2, w, p + "mlp.", layer["mlp"])
+                f = mixture_of_experts(h2, w, p + "mlp.", layer["mlp"], margins)
             total = total + f * w[p + "ls2"]
         x = x + m * total
         if layers_out is not None:
             layers_out.append(x.clone())
     z = tanh_norm(x, w, "final.norm") @ w["head"].T
-    return soft_cap(z, cfg["logit_softcap"])
+    return soft_cap(z, cfg["logit_softcap"]) if cfg.get("logit_softcap") else z
 
 
 class PlainNibelix:
@@ -188,8 +203,22 @@ class PlainNibelix:
             self.cfg = json.load(f)
         self.w = read_weights(model_dir)
 
+        self._memo: dict = {}
+
+    def run(self, tokens: List[int]) -> Tuple[torch.Tensor, float]:
+        """(logits, the smallest margin of any router's choice over the sequence; infinite without routers)."""
+        key = tuple(tokens)
+        if key not in self._memo:
+            margins: list = []
+            self._memo[key] = (forward(self.cfg, self.w, tokens, None, margins), min(margins, default=float("inf")))
+        return self._memo[key]
+
     def logits(self, tokens: List[int]) -> torch.Tensor:
-        return forward(self.cfg, self.w, tokens)
+        return self.run(tokens)[0]
+
+    def closest_call(self, tokens: List[int]) -> float:
+        """The smallest margin of any router's choice over the sequence (infinite without routers)."""
+        return self.run(tokens)[1]
 
     def layers(self, tokens: List[int]) -> torch.Tensor:
         out: list = []
@@ -199,5 +228,5 @@ class PlainNibelix:
     def greedy(self, prompt: List[int], n: int) -> List[int]:
         toks = list(prompt)
         for _ in range(n):
-            toks.append(int(torch.argmax(self.logits(toks)[-1])))
+            toks.append(int(torch.argmax(forward(self.cfg, self.w, toks)[-1])))
         return toks[len(prompt):]

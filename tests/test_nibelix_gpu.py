@@ -1,0 +1,383 @@
+"""The Nibelix decoder in the engine against the plain implementation (tests/plain_nibelix.py): each mechanism alone,
+whole prompts against token-by-token decoding, portions, unequal batches with slots, pages and state rows used again,
+keys far back, at page borders and on both sides of a window's edge, first tokens, long decoding, generation through
+the entry point, the replay program; float32 and bfloat16, on configurations that differ in every size and option.
+
+Routers: a token whose choice between two experts is nearly a tie may choose the other way when its input carries
+bfloat16 rounding, and then that position's logits differ by far more than rounding.  float32 runs are compared at
+every position (requests whose closest choice in the plain implementation is nearer than 1e-4 are drawn again);
+bfloat16 runs of configurations with routers may have a small share of positions beyond the bound, and the rest must
+be well within it.
+"""
+import json
+import os
+import shutil
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+from helpers import TOL, batched_trace, random_requests, rel_err, run_trace, tail_trace, whole_trace
+from nibelix_configs import CONFIGS, ROUTED, make_nibelix
+from plain_nibelix import PlainNibelix
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+DTYPES = ["float32", "bfloat16"]
+LENGTHS = {"mixed": [1, 2, 9, 64, 65, 150], "odd": [1, 3, 20, 64, 66, 131], "wide": [3, 17, 63, 128, 129, 300]}
+ONLY_LENGTHS = [1, 2, 31, 64, 129, 140]
+FLIP_SHARE = 0.15         # bfloat16 with routers: positions that may be beyond the bound
+
+
+@pytest.fixture(scope="module")
+def folders(tmp_path_factory):
+    root = tmp_path_factory.mktemp("nibelix")
+    return {name: make_nibelix(name, str(root / name)) for name in CONFIGS}
+
+
+_plain = {}
+
+
+def plain(folder):
+    if folder not in _plain:
+        _plain[folder] = PlainNibelix(folder)
+    return _plain[folder]
+
+
+def engine_for(folder, dtype, max_tokens=2048):
+    from exl3_server_b200 import Engine
+    return Engine.from_folder(folder, dtype=dtype, max_tokens=max_tokens)
+
+
+def requests_for(name, folder, lengths, seed):
+    """Random requests none of whose routers' choices is a close call in the plain implementation."""
+    pm = plain(folder)
+    out = {}
+    for i, n in enumerate(lengths):
+        for attempt in range(20):
+            toks = random_requests(CONFIGS[name].vocab, [n], seed=seed + 1000 * i + 17 * attempt)["r0"]
+            if pm.closest_call(toks) >= 1e-4:
+                break
+        out[f"r{i}"] = toks
+    return out
+
+
+def position_errors(got, want):
+    return np.max(np.abs(got.astype(np.float64) - want.astype(np.float64)), axis=1) / max(1e-30, np.max(np.abs(want)))
+
+
+def close_enough(got, want, dtype, name, what):
+    assert got.shape == want.shape, what
+    assert np.isfinite(got).all(), what
+    err = position_errors(got, want)
+    bad = err > TOL[dtype]
+    if dtype == "bfloat16" and name in ROUTED:
+        assert bad.mean() <= FLIP_SHARE and np.median(err) <= TOL[dtype] / 3, \
+            f"{what}: {bad.sum()} of {len(err)} positions beyond the bound, median error {np.median(err):.3e}"
+        return
+    assert not bad.any(), (f"{what}: differs from the plain implementation by {err.max():.3e} (bound {TOL[dtype]:.0e}); "
+                           f"first wrong position {int(np.argmax(bad))} of {len(err)}")
+
+
+def check(got, want, dtype, name, what):
+    assert set(got) == set(want)
+    for rid in want:
+        close_enough(got[rid], want[rid], dtype, name, f"{what}, request {rid}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_decoded_and_batched(folders, name, dtype):
+    folder = folders[name]
+    requests = requests_for(name, folder, LENGTHS.get(name, ONLY_LENGTHS), seed=3)
+    pm = plain(folder)
+    want = {rid: pm.logits(t).numpy() for rid, t in requests.items()}
+    eng = engine_for(folder, dtype)
+    check(run_trace(eng, whole_trace(requests)), want, dtype, name, "whole")
+    check(run_trace(eng, tail_trace(requests, 45)), want, dtype, name, "last 45 one by one")
+    # everything but the first token decoded: the prompt path and the one-token path must walk the same sums
+    short = {rid: t for rid, t in requests.items() if len(t) <= 70}
+    check(run_trace(eng, tail_trace(short, 1000)), {rid: want[rid] for rid in short}, dtype, name, "token by token")
+    ids = list(requests)
+    # two batches one after the other, so that slots, pages and state rows are used again
+    batches = [[ids[5], ids[0], ids[2], ids[3]], [ids[1], ids[4], ids[0]]]
+    prompt_len = {rid: max(1, len(requests[rid]) - k) for rid, k in zip(ids, (0, 1, 4, 40, 33, 70))}
+    check(run_trace(eng, batched_trace(requests, batches, prompt_len)),
+          {rid: want[rid] for b in batches for rid in b}, dtype, name, "batched")
+    assert eng.cache.tokens_held() == 0
+    eng.check_kernels()
+
+
+@pytest.mark.parametrize("name", ["mixed", "wide"])
+def test_float32_cuttings_agree_closely(folders, name):
+    requests = requests_for(name, folders[name], LENGTHS[name], seed=5)
+    eng = engine_for(folders[name], "float32")
+    a = run_trace(eng, whole_trace(requests))
+    b = run_trace(eng, tail_trace(requests, 32))
+    for rid in requests:
+        assert rel_err(b[rid], a[rid]) <= 2e-6, rid
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mixed", "odd", "wide"])
+def test_portions_of_a_prompt(folders, name, dtype):
+    """A prompt fed in portions of many sizes, down to two tokens, some ending on a page border, on a window's edge
+    and inside one, and one long enough for the recurrence's chunks to run side by side and for the experts to take
+    the many-rows product."""
+    from exl3_server_b200 import StepEntry
+    folder = folders[name]
+    toks = requests_for(name, folder, [430], seed=9)["r0"]
+    want = plain(folder).logits(toks).numpy()
+    eng = engine_for(folder, dtype)
+    for cuts in ([2, 2, 60, 3, 61, 2, 100, 200], [64, 64, 2, 37, 63, 200], [7, 121, 2, 2, 2, 96, 199, 1], [429, 1],
+                 [50, 50, 50, 130, 150], [1, 300, 129]):
+        assert sum(cuts) == len(toks)
+        s = eng.open()
+        got, at = [], 0
+        for n in cuts:
+            got.append(eng.step([StepEntry(s, toks[at:at + n], "all")]).float().cpu().numpy())
+            at += n
+        eng.close(s)
+        close_enough(np.concatenate(got), want, dtype, name, f"portions {cuts}")
+    assert eng.cache.tokens_held() == 0
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_unequal_portions_in_one_batch(folders, dtype):
+    """Rows that go on by portions of different sizes in the same steps, beside a row that starts."""
+    from exl3_server_b200 import StepEntry
+    folder = folders["mixed"]
+    reqs = requests_for("mixed", folder, [150, 90, 40], seed=13)
+    pm = plain(folder)
+    want = {r: pm.logits(t).numpy() for r, t in reqs.items()}
+    eng = engine_for(folder, dtype)
+    sa, sb = eng.open(), eng.open()
+    got = {r: [] for r in reqs}
+    out = eng.step([StepEntry(sa, reqs["r0"][:70], "all"), StepEntry(sb, reqs["r1"][:3], "all")]).float().cpu().numpy()
+    got["r0"].append(out[:70]); got["r1"].append(out[70:])
+    sc = eng.open()
+    out = eng.step([StepEntry(sb, reqs["r1"][3:66], "all"), StepEntry(sc, reqs["r2"], "all"),
+                    StepEntry(sa, reqs["r0"][70:72], "all")]).float().cpu().numpy()
+    got["r1"].append(out[:63]); got["r2"].append(out[63:103]); got["r0"].append(out[103:])
+    eng.close(sc)
+    out = eng.step([StepEntry(sa, reqs["r0"][72:], "all"), StepEntry(sb, reqs["r1"][66:], "all")]).float().cpu().numpy()
+    got["r0"].append(out[:78]); got["r1"].append(out[78:])
+    for r in reqs:
+        close_enough(np.concatenate(got[r]), want[r], dtype, "mixed", r)
+
+
+def _marked_model(src, folder, name):
+    """A copy of a one-layer attention model in which one token's key stands out for every query, in the first map
+    only.  Feature 0 of the model is on for the marked token only and feature 1 for every token (the other embedding
+    features stay random); the norm passes both; the key matrix sends feature 0, and the query matrix feature 1, to
+    the same features of the first map of every head (its second half, which the partial rotation leaves alone), so
+    the marked key's score in that map is far above the spread of the others' wherever the query stands, while the
+    second map stays an ordinary average."""
+    from safetensors import safe_open
+    from exl3_server_b200.weights.safetensors_io import write_safetensors
+    os.makedirs(folder)
+    shutil.copy(os.path.join(src, "config.json"), folder)
+    with safe_open(os.path.join(src, "model.safetensors"), framework="pt") as f:
+        tensors = {k: f.get_tensor(k).float() for k in f.keys()}
+    marked = 77
+    tensors["embed"][:, 0] = 0.0
+    tensors["embed"][:, 1] = 0.5
+    tensors["embed"][marked, 0] = 2.0
+    tensors["l0.norm1"][:2] = 1.0
+    tensors["l0.norm1.b"][:2] = 0.0
+    d = CONFIGS[name].layers[0].mixer["dim"]
+    for w, col in ((tensors["l0.mix.q"], 1), (tensors["l0.mix.k"], 0)):
+        w[:, col] = 0.0
+        w.view(-1, 2, d, w.shape[1])[:, 0, d // 2:, col] = 4.0
+    write_safetensors(os.path.join(folder, "model.safetensors"), ((k, v.to(torch.bfloat16)) for k, v in tensors.items()),
+                      metadata={"format": "pt"})
+    return marked
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name, places", [("only_full_attention", [0, 1, 63, 64, 127, 128, 300]),
+                                           ("only_attention", [610, 611, 629, 630, 631, 639, 640, 690, 699]),
+                                           ("only_attention_64", [610, 611, 629, 630, 631, 639, 640, 690, 699])])
+def test_a_key_that_stands_out(folders, tmp_path, name, places, dtype):
+    """The marked key sits first, second, on both sides of page borders and hundreds of tokens back (no window), and
+    around the edge of the window of 70 positions: the last query (699) sees 630 .. 699, the twenty before it see
+    from 610 .. 629 on; losing the key, reading a neighbour instead or seeing it across the edge changes the logits
+    by far more than the bound.  Whole prompts, and the last 95 tokens decoded one by one, so that the window passes
+    over the key while decoding."""
+    folder = str(tmp_path / "m")
+    marked = _marked_model(folders[name], folder, name)
+    pm = PlainNibelix(folder)
+    vocab = CONFIGS[name].vocab
+    base = [t if t != marked else 5 for t in random_requests(vocab, [700], seed=21)["r0"]]
+    window = (CONFIGS[name].layers[0].mixer.get("mask") or {}).get("size", 10 ** 9)
+    eng = engine_for(folder, dtype)
+    for place in places:
+        toks = list(base)
+        toks[place] = marked
+        want = pm.logits(toks).numpy()
+        seen = [q for q in range(680, 700) if 0 <= q - place < window]
+        unseen = [q for q in range(680, 700) if q - place >= window]
+        plainly = pm.logits(base).numpy()
+        if seen:
+            assert rel_err(plainly[seen], want[seen]) > 0.2, place      # the test can see the key
+        if unseen:
+            assert rel_err(plainly[unseen], want[unseen]) < 1e-9, place  # and the window hides it
+        got = run_trace(eng, whole_trace({"a": toks}))["a"]
+        assert rel_err(got, want) <= TOL[dtype], ("whole", place)
+        got = run_trace(eng, tail_trace({"a": toks}, 95))["a"]
+        assert rel_err(got, want) <= TOL[dtype], ("decoded", place)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_token_far_back_in_the_state(folders, tmp_path, dtype):
+    """One token 600 positions back, whose key and value are large, among small ones: with the slowest decay
+    (0.9995) its mark is still a third of the state; a state that is lost, reset or decayed once too often shows."""
+    from safetensors import safe_open
+    from exl3_server_b200.weights.safetensors_io import write_safetensors
+    src, folder = folders["only_lightning"], str(tmp_path / "m")
+    os.makedirs(folder)
+    shutil.copy(os.path.join(src, "config.json"), folder)
+    with safe_open(os.path.join(src, "model.safetensors"), framework="pt") as f:
+        tensors = {k: f.get_tensor(k).float() for k in f.keys()}
+    marked = 77
+    tensors["embed"] *= 0.3
+    tensors["embed"][marked] *= 40.0
+    write_safetensors(os.path.join(folder, "model.safetensors"), ((k, v.to(torch.bfloat16)) for k, v in tensors.items()),
+                      metadata={"format": "pt"})
+    pm = PlainNibelix(folder)
+    base = [t if t != marked else 5 for t in random_requests(128, [700], seed=27)["r0"]]
+    toks = list(base)
+    toks[90] = marked
+    want = pm.logits(toks).numpy()
+    assert rel_err(pm.logits(base).numpy()[-20:], want[-20:]) > 0.05
+    eng = engine_for(folder, dtype)
+    assert rel_err(run_trace(eng, whole_trace({"a": toks}))["a"], want) <= TOL[dtype]
+    assert rel_err(run_trace(eng, tail_trace({"a": toks}, 64))["a"], want) <= TOL[dtype]
+    from exl3_server_b200 import StepEntry
+    s = eng.open()
+    got = [eng.step([StepEntry(s, toks[a:b], "all")]).float().cpu().numpy()
+           for a, b in ((0, 89), (89, 91), (91, 300), (300, 302), (302, 700))]
+    eng.close(s)
+    assert rel_err(np.concatenate(got), want) <= TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["mixed", "odd", "wide"])
+def test_long_decoding(folders, name, dtype):
+    """Three tokens of prompt, then 200 decoded one by one over three page borders and past every window, two
+    sequences side by side."""
+    from exl3_server_b200 import StepEntry
+    folder = folders[name]
+    reqs = requests_for(name, folder, [203, 180], seed=17)
+    pm = plain(folder)
+    want = [pm.logits(reqs["r0"]).numpy(), pm.logits(reqs["r1"]).numpy()]
+    eng = engine_for(folder, dtype)
+    s = [eng.open(), eng.open()]
+    got = [[], []]
+    out = eng.step([StepEntry(s[0], reqs["r0"][:3], "all"), StepEntry(s[1], reqs["r1"][:3], "all")]).float().cpu().numpy()
+    got[0].append(out[:3]); got[1].append(out[3:])
+    for i in range(3, 203):
+        live = [k for k in (0, 1) if i < len(reqs[f"r{k}"])]
+        out = eng.step([StepEntry(s[k], [reqs[f"r{k}"][i]], "all") for k in live]).float().cpu().numpy()
+        for j, k in enumerate(live):
+            got[k].append(out[j:j + 1])
+    for k in (0, 1):
+        close_enough(np.concatenate(got[k]), want[k], dtype, name, k)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_a_reused_slot_shows_nothing_of_its_former_owner(folders, dtype):
+    """A sequence's state rows and pages go to the next sequence; the next one must start from zero state and see
+    none of the old rows, also when it is shorter than the old one."""
+    from exl3_server_b200 import StepEntry
+    folder = folders["mixed"]
+    reqs = requests_for("mixed", folder, [190, 30], seed=23)
+    want = plain(folder).logits(reqs["r1"]).numpy()
+    eng = engine_for(folder, dtype, max_tokens=256)
+    for _ in range(3):
+        s = eng.open()
+        eng.step([StepEntry(s, reqs["r0"], None)])
+        eng.close(s)
+        s2 = eng.open()
+        assert s2 == s
+        got = [eng.step([StepEntry(s2, reqs["r1"][:9], "all")]).float().cpu().numpy()]
+        for t in reqs["r1"][9:]:
+            got.append(eng.step([StepEntry(s2, [t], "all")]).float().cpu().numpy())
+        eng.close(s2)
+        close_enough(np.concatenate(got), want, dtype, "mixed", "after reuse")
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("name", ["mixed", "odd", "wide"])
+def test_greedy_generation_through_the_entry_point(folders, name):
+    from exl3_server_b200 import GenerateOptions
+    folder = folders[name]
+    prompts = list(requests_for(name, folder, [5, 70, 1, 33], seed=29).values())
+    eng = engine_for(folder, "float32")
+    res = eng.generate(prompts, GenerateOptions(max_tokens=24, ignore_eos=True, max_batch=3))
+    pm = plain(folder)
+    for p, r in zip(prompts, res):
+        assert r.tokens == pm.greedy(p, 24)
+        assert r.finish_reason == "length"
+    assert eng.cache.tokens_held() == 0
+    # bfloat16: the same call runs and every token is in range (near-ties may fall the other way)
+    eng = engine_for(folder, "bfloat16")
+    res = eng.generate(prompts, GenerateOptions(max_tokens=24, ignore_eos=True))
+    assert all(len(r.tokens) == 24 and all(0 <= t < CONFIGS[name].vocab for t in r.tokens) for r in res)
+    eng.check_kernels()
+
+
+@pytest.mark.parametrize("name", ["mixed", "odd"])
+def test_residual_stream_layer_by_layer(folders, name):
+    """The float32 residual after every layer against the plain implementation's."""
+    from exl3_server_b200 import StepEntry
+    folder = folders[name]
+    toks = requests_for(name, folder, [75], seed=31)["r0"]
+    want = plain(folder).layers(toks)
+    eng = engine_for(folder, "float32")
+    seen = []
+    for b in eng.model.blocks:
+        def wrapped(stream, *args, f=b.forward, **kwargs):
+            f(stream, *args, **kwargs)
+            seen.append(stream.h.clone())
+        b.forward = wrapped
+    s = eng.open()
+    eng.step([StepEntry(s, toks, None)])
+    assert len(seen) == len(want)
+    for i, (a, b) in enumerate(zip(seen, want)):
+        assert rel_err(a.cpu().numpy(), b.numpy()) <= 1e-5, i
+
+
+def test_replay_program_and_command_line(folders, tmp_path):
+    folder = folders["mixed"]
+    vocab = CONFIGS["mixed"].vocab
+    reqs = requests_for("mixed", folder, [40, 7], seed=4)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": reqs["r0"][:38], "want": [0, 37]},
+                                {"id": "b", "tokens": reqs["r1"][:6], "want": []}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": [reqs["r0"][38]], "want": [0]},
+                                {"id": "b", "tokens": [reqs["r1"][6]], "want": [0]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": [reqs["r0"][39]], "want": []}], "end": ["a"]},
+        {"step": 3, "entries": [{"id": "b", "tokens": reqs["r1"], "want": [6]}], "end": ["b"]},
+    ]
+    pm = plain(folder)
+    la, lb = pm.logits(reqs["r0"]).numpy(), pm.logits(reqs["r1"]).numpy()
+    out = tmp_path / "float32"
+    p = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", folder, "--dtype", "float32",
+                        "--out", str(out), "--max-tokens", "128"],
+                       input="\n".join(json.dumps(s) for s in steps) + "\n", capture_output=True, text=True,
+                       timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert p.stdout.split() == ["done", "0", "done", "1", "done", "2", "done", "3"]
+    s0 = np.fromfile(out / "0.f32", dtype="<f4").reshape(-1, vocab)
+    s1 = np.fromfile(out / "1.f32", dtype="<f4").reshape(-1, vocab)
+    s3 = np.fromfile(out / "3.f32", dtype="<f4").reshape(-1, vocab)
+    assert rel_err(s0, la[[0, 37]]) <= TOL["float32"]
+    assert rel_err(s1, np.stack([la[38], lb[6]])) <= TOL["float32"]
+    assert rel_err(s3, lb[6:7]) <= TOL["float32"]
+    p = subprocess.run([sys.executable, "-m", "exl3_server_b200", "--model", folder, "-p", "5,6,7", "--max-tokens", "5",
+                        "--ignore-eos", "--dtype", "float32"], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert p.returncode == 0, p.stderr[-2000:]
+    assert p.stdout.strip() == ",".join(map(str, pm.greedy([5, 6, 7], 5)))
