@@ -422,9 +422,11 @@ def designs(args) -> int:
             if args.design_part in ("both", "decode"):
                 ms, launches, kv = rig.decode(B, C, steps, warm)
                 kv = B * rig.context_bytes(C - steps // 2)
-                gbs = (rig.model.weight_bytes() + kv) / (ms / steps / 1e3) / 1e9
-                r.update(decode_ms_per_step=ms / steps, decode_tok_s=B * steps / (ms / 1e3), decode_gb_s=gbs,
-                         decode_hbm_frac=gbs / hbm_gbs, gpu_launches_per_step=int(launches) // steps)
+                step_weights = rig.model.weight_bytes(B)      # of routed experts, the ones a step of B tokens picks
+                gbs = (step_weights + kv) / (ms / steps / 1e3) / 1e9
+                r.update(decode_weight_bytes=step_weights, decode_ms_per_step=ms / steps,
+                         decode_tok_s=B * steps / (ms / 1e3), decode_gb_s=gbs, decode_hbm_frac=gbs / hbm_gbs,
+                         gpu_launches_per_step=int(launches) // steps)
             rec[arch] = r
             rig.close()
         out["sizes"][name] = rec

@@ -38,7 +38,10 @@ __device__ inline float da_rotated(const void* x, int dtype, int64_t base, int i
   return v * cs[i - half] + da_ld(x, dtype, base + i - half) * sn[i - half];
 }
 
-__global__ void __launch_bounds__(256)
+// A block takes MP_ITEMS outputs of one token: the widened queries first, then the key rows, then the value rows.
+constexpr int MP_THREADS = 256, MP_ITEMS = 2048;
+
+__global__ void __launch_bounds__(MP_THREADS)
 maps_prep_kernel(const void* x, int x_dtype, int64_t ld, int q_off, int k_off, int v_off, int nh, int nkv, int maps, int d,
                  int dv, int row, int v_row, int rot, const float* __restrict__ f_hi, const float* __restrict__ f_lo,
                  const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride, int page, void* q_out,
@@ -54,31 +57,103 @@ maps_prep_kernel(const void* x, int x_dtype, int64_t ld, int q_off, int k_off, i
   for (int i = threadIdx.x; i < half; i += blockDim.x) rope_sincos((float)pos, f_hi[i], f_lo[i], sn + i, cs + i);
   __syncthreads();
   const int64_t xb = (int64_t)t * ld;
-  // queries: head h, map m -> head h * maps + m, features [m * d, m * d + d) of `row`, zero elsewhere
   const int nq = nh * maps;
-  for (int idx = threadIdx.x; idx < nq * row; idx += blockDim.x) {
-    const int vh = idx / row, c = idx - vh * row;
-    const int m = vh % maps;
-    float v = 0.0f;
-    if (c >= m * d && c < m * d + d) v = da_rotated(x, x_dtype, xb + q_off + (int64_t)vh * d, c - m * d, rot, sn, cs);
-    da_st(q_out, q_dtype, (int64_t)t * nq * row + idx, v);
-  }
+  const int n_q = nq * row, n_k = nkv * row, n_v = nkv * v_row;
   const int pg = __ldcg(block_table + (int64_t)__ldcg(tok_seq + t) * bt_stride + pos / page);
-  if (pg < 0) return;
   const int slot = pos % page;
-  for (int idx = threadIdx.x; idx < nkv * row; idx += blockDim.x) {
-    const int g = idx / row, c = idx - g * row;
-    float v = 0.0f;
-    if (c < maps * d) {
-      const int m = c / d;
-      v = da_rotated(x, x_dtype, xb + k_off + ((int64_t)g * maps + m) * d, c - m * d, rot, sn, cs);
+  const int first = blockIdx.y * MP_ITEMS;
+  const int last = min(first + MP_ITEMS, n_q + n_k + n_v);
+  for (int item = first + threadIdx.x; item < last; item += MP_THREADS) {
+    if (item < n_q) {
+      // queries: head h, map m -> head h * maps + m, features [m * d, m * d + d) of `row`, zero elsewhere
+      const int vh = item / row, c = item - vh * row;
+      const int m = vh % maps;
+      float v = 0.0f;
+      if (c >= m * d && c < m * d + d) v = da_rotated(x, x_dtype, xb + q_off + (int64_t)vh * d, c - m * d, rot, sn, cs);
+      da_st(q_out, q_dtype, (int64_t)t * n_q + item, v);
+    } else if (pg < 0) {
+      continue;
+    } else if (item < n_q + n_k) {
+      const int idx = item - n_q;
+      const int g = idx / row, c = idx - g * row;
+      float v = 0.0f;
+      if (c < maps * d) {
+        const int m = c / d;
+        v = da_rotated(x, x_dtype, xb + k_off + ((int64_t)g * maps + m) * d, c - m * d, rot, sn, cs);
+      }
+      da_st(k_pool, pool_dtype, (((int64_t)pg * nkv + g) * page + slot) * row + c, v);
+    } else {
+      const int idx = item - n_q - n_k;
+      const int g = idx / v_row, c = idx - g * v_row;
+      const float v = c < dv ? da_ld(x, x_dtype, xb + v_off + (int64_t)g * dv + c) : 0.0f;
+      da_st(v_pool, pool_dtype, (((int64_t)pg * nkv + g) * page + slot) * v_row + c, v);
     }
-    da_st(k_pool, pool_dtype, (((int64_t)pg * nkv + g) * page + slot) * row + c, v);
   }
-  for (int idx = threadIdx.x; idx < nkv * v_row; idx += blockDim.x) {
-    const int g = idx / v_row, c = idx - g * v_row;
-    const float v = c < dv ? da_ld(x, x_dtype, xb + v_off + (int64_t)g * dv + c) : 0.0f;
-    da_st(v_pool, pool_dtype, (((int64_t)pg * nkv + g) * page + slot) * v_row + c, v);
+}
+
+// The same for bfloat16 throughout with every size a multiple of 8 (d, rot / 2, dv, the rows, the offsets, the row
+// pitch): a thread takes 8 neighbouring outputs with 16-byte loads and stores.
+__device__ inline void mp_rot8(const __nv_bfloat16* src, int i, int rot, const float* sn, const float* cs, float (&v)[8]) {
+  load_vec_cg(src + i, v);
+  if (i >= rot) return;
+  const int half = rot >> 1;
+  float o[8];
+  if (i < half) {
+    load_vec_cg(src + i + half, o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = v[j] * cs[i + j] - o[j] * sn[i + j];
+  } else {
+    load_vec_cg(src + i - half, o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = v[j] * cs[i - half + j] + o[j] * sn[i - half + j];
+  }
+}
+
+__global__ void __launch_bounds__(MP_THREADS)
+maps_prep_vec_kernel(const __nv_bfloat16* x, int64_t ld, int q_off, int k_off, int v_off, int nh, int nkv, int maps, int d,
+                     int dv, int row, int v_row, int rot, const float* __restrict__ f_hi, const float* __restrict__ f_lo,
+                     const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride, int page,
+                     __nv_bfloat16* q_out, __nv_bfloat16* k_pool, __nv_bfloat16* v_pool) {
+  extern __shared__ float sc[];                    // [rot / 2] sines, [rot / 2] cosines
+  pdl_wait();
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int pos = __ldcg(tok_pos + t);
+  const int half = rot >> 1;
+  float* sn = sc;
+  float* cs = sc + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) rope_sincos((float)pos, f_hi[i], f_lo[i], sn + i, cs + i);
+  __syncthreads();
+  const __nv_bfloat16* xt = x + (int64_t)t * ld;
+  const int nq = nh * maps;
+  const int n_q = nq * row, n_k = nkv * row, n_v = nkv * v_row;
+  const int pg = __ldcg(block_table + (int64_t)__ldcg(tok_seq + t) * bt_stride + pos / page);
+  const int slot = pos % page;
+  const int first = blockIdx.y * MP_ITEMS;
+  const int last = min(first + MP_ITEMS, n_q + n_k + n_v);
+  for (int item = first + threadIdx.x * 8; item < last; item += MP_THREADS * 8) {
+    float v[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+    if (item < n_q) {
+      const int vh = item / row, c = item - vh * row;
+      const int m = vh % maps;
+      if (c >= m * d && c < m * d + d) mp_rot8(xt + q_off + (int64_t)vh * d, c - m * d, rot, sn, cs, v);
+      store_vec(q_out + (int64_t)t * n_q + item, v);
+    } else if (pg < 0) {
+      continue;
+    } else if (item < n_q + n_k) {
+      const int idx = item - n_q;
+      const int g = idx / row, c = idx - g * row;
+      if (c < maps * d) {
+        const int m = c / d;
+        mp_rot8(xt + k_off + ((int64_t)g * maps + m) * d, c - m * d, rot, sn, cs, v);
+      }
+      store_vec(k_pool + (((int64_t)pg * nkv + g) * page + slot) * row + c, v);
+    } else {
+      const int idx = item - n_q - n_k;
+      const int g = idx / v_row, c = idx - g * v_row;
+      if (c < dv) load_vec_cg(xt + v_off + (int64_t)g * dv + c, v);
+      store_vec(v_pool + (((int64_t)pg * nkv + g) * page + slot) * v_row + c, v);
+    }
   }
 }
 
@@ -125,9 +200,21 @@ extern "C" int exl3_maps_prep(const void* x, int x_dtype, int64_t ld, int q_off,
               dv, row, v_row, rot);
     return ERR_BAD_ARGUMENT;
   }
-  launch_pdl(maps_prep_kernel, dim3(T), dim3(256), (size_t)rot * sizeof(float), stream, x, x_dtype, ld, q_off, k_off,
-             v_off, nh, nkv, maps, d, dv, row, v_row, rot, f_hi, f_lo, tok_pos, tok_seq, block_table, bt_stride, page,
-             q_out, q_dtype, k_pool, v_pool, pool_dtype);
+  const int items = nh * maps * row + nkv * row + nkv * v_row;
+  if (ceil_div(items, MP_ITEMS) > 65535) { set_error("maps_prep: rows too wide"); return ERR_UNSUPPORTED; }
+  const bool vec = x_dtype == DT_BF16 && q_dtype == DT_BF16 && pool_dtype == DT_BF16 && d % 8 == 0 && (rot >> 1) % 8 == 0 &&
+                   dv % 8 == 0 && row % 8 == 0 && v_row % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
+                   ld % 8 == 0 && aligned16(x) && aligned16(q_out) && aligned16(k_pool) && aligned16(v_pool);
+  if (vec) {
+    launch_pdl(maps_prep_vec_kernel, dim3(T, ceil_div(items, MP_ITEMS)), dim3(MP_THREADS), (size_t)rot * sizeof(float),
+               stream, static_cast<const __nv_bfloat16*>(x), ld, q_off, k_off, v_off, nh, nkv, maps, d, dv, row, v_row, rot,
+               f_hi, f_lo, tok_pos, tok_seq, block_table, bt_stride, page, static_cast<__nv_bfloat16*>(q_out),
+               static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool));
+    return launch_status("maps_prep");
+  }
+  launch_pdl(maps_prep_kernel, dim3(T, ceil_div(items, MP_ITEMS)), dim3(MP_THREADS), (size_t)rot * sizeof(float), stream,
+             x, x_dtype, ld, q_off, k_off, v_off, nh, nkv, maps, d, dv, row, v_row, rot, f_hi, f_lo, tok_pos, tok_seq,
+             block_table, bt_stride, page, q_out, q_dtype, k_pool, v_pool, pool_dtype);
   return launch_status("maps_prep");
 }
 

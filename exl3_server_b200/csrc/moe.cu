@@ -22,7 +22,7 @@ namespace exl3 {
 
 constexpr int RT_TOK = 4;        // tokens a block of the router takes (one a warp for the choice)
 constexpr int RT_WARPS = 16;     // warps of a block: router outputs go round over them
-constexpr int RT_KC = 512;       // columns of x staged at a time
+constexpr int RT_KC = 512;       // columns of a piece: what a warp reads of a router row at a time
 constexpr int MOE_TM = 32;       // rows of a tile
 constexpr int MOE_TN = 64;       // output features of a block
 constexpr int MOE_TK = 32;
@@ -48,12 +48,14 @@ __device__ inline void warp_argmax(float& v, int& i) {
 template <typename TX>
 __global__ void __launch_bounds__(RT_WARPS * 32)
 moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const float* __restrict__ corr, int T, int W,
-                 int E, int S, int groups, int keep, int top, float scale, int score_kind, int* idx, float* wt,
-                 float* gate_out) {
+                 int E, int S, int groups, int keep, int top, float scale, int score_kind, int stage_cols, int* idx,
+                 float* wt, float* gate_out) {
   extern __shared__ float rs[];
   const int R = E + S;
-  float* xs = rs;                                  // [RT_TOK][RT_KC]
-  float* z = xs + RT_TOK * RT_KC;                  // [RT_TOK][R]   logits, then scores
+  const int pieces = (stage_cols + RT_KC - 1) / RT_KC;   // pieces of RT_KC columns in what is staged at a time
+  float* xs = rs;                                  // [RT_TOK][stage_cols]
+  float* zp = xs + RT_TOK * stage_cols;            // [pieces][RT_TOK][R]  partial sums of the staged columns
+  float* z = zp + pieces * RT_TOK * R;             // [RT_TOK][R]   logits, then scores
   float* c = z + RT_TOK * R;                       // [RT_TOK][E]   choice scores
   float* gs = c + RT_TOK * E;                      // [RT_TOK][groups] group scores
   float* gk = gs + RT_TOK * groups;                // [RT_TOK][groups] 1: the group is kept
@@ -62,33 +64,44 @@ moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const f
   const int t0 = blockIdx.x * RT_TOK;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < RT_TOK * R; i += blockDim.x) z[i] = 0.0f;
-  for (int k0 = 0; k0 < W; k0 += RT_KC) {
-    const int kc = min(RT_KC, W - k0);
+  // Columns are staged stage_cols at a time (all of them when they fit); a warp takes (output, piece) pairs, so that
+  // the pieces of a row are read side by side; the pieces' sums are added in their order.
+  for (int k0 = 0; k0 < W; k0 += stage_cols) {
+    const int kc = min(stage_cols, W - k0);
     __syncthreads();
-    for (int i = threadIdx.x; i < RT_TOK * RT_KC; i += blockDim.x) {
-      const int tok = i / RT_KC, col = i - tok * RT_KC;
+    for (int i = threadIdx.x; i < RT_TOK * stage_cols; i += blockDim.x) {
+      const int tok = i / stage_cols, col = i - tok * stage_cols;
       xs[i] = (t0 + tok < T && col < kc) ? moe_ld(x + (int64_t)(t0 + tok) * ldx + k0 + col) : 0.0f;
     }
     __syncthreads();
-    for (int e = warp; e < R; e += RT_WARPS) {
-      const float* wrow = wr + (int64_t)e * W + k0;
+    for (int item = warp; item < R * pieces; item += RT_WARPS) {
+      const int e = item / pieces, pc = item - e * pieces;
+      const int c0 = pc * RT_KC;
+      const float* wrow = wr + (int64_t)e * W + k0 + c0;
       float part[RT_TOK];
 #pragma unroll
       for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = 0.0f;
-      // a fixed number of rounds, so that the row's loads are all under way before the first is used
+      // a fixed number of rounds, so that the piece's loads are all under way before the first is used
       float wv[RT_KC / 32];
 #pragma unroll
-      for (int i = 0; i < RT_KC / 32; ++i) wv[i] = lane + 32 * i < kc ? wrow[lane + 32 * i] : 0.0f;
+      for (int i = 0; i < RT_KC / 32; ++i) wv[i] = c0 + lane + 32 * i < kc ? wrow[lane + 32 * i] : 0.0f;
 #pragma unroll
       for (int i = 0; i < RT_KC / 32; ++i) {
+        const int col = min(c0 + lane + 32 * i, stage_cols - 1);
 #pragma unroll
-        for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = fmaf(wv[i], xs[tok * RT_KC + lane + 32 * i], part[tok]);
+        for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = fmaf(wv[i], xs[tok * stage_cols + col], part[tok]);
       }
 #pragma unroll
       for (int tok = 0; tok < RT_TOK; ++tok) {
         const float s = warp_sum(part[tok]);
-        if (lane == 0) z[tok * R + e] += s;
+        if (lane == 0) zp[(pc * RT_TOK + tok) * R + e] = s;
       }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < RT_TOK * R; i += blockDim.x) {
+      float s = z[i];
+      for (int pc = 0; pc < pieces; ++pc) s += zp[pc * RT_TOK * R + i];
+      z[i] = s;
     }
   }
   __syncthreads();
@@ -274,16 +287,19 @@ moe_gemm_kernel(const TA* A, int64_t lda, int a_div, const TW* __restrict__ Wt, 
 
 // ---- a few rows per expert (decode): the experts' matrices are read once, a warp per output feature ---------------
 //
-// out[p, n] = act(sum_k A[p / a_div, k] * W[e(p), n, k]) for tiles of at most MV_ROWS pairs: a warp takes MV_FEAT output
-// features, reads their rows of W in 16-byte pieces (all features' loads under way together) and keeps one float32
-// sum per (feature, pair); lanes' sums meet in a fixed order, so a pair's result does not depend on its tile mates.
-constexpr int MV_ROWS = 8, MV_FEAT = 4, MV_WARPS = 8;
+// out[p, n] = act(sum_k A[p / a_div, k] * W[e(p), n, k]) for tiles of at most MV_ROWS pairs.  K is walked in pieces
+// of MV_KC columns: the block puts the tile's rows of A for the piece into shared memory, and every warp takes
+// MV_FEAT output features, whose rows of W it reads in 16-byte pieces, all of a piece's loads under way before the
+// first is used.  One float32 sum per (feature, pair) and lane; the lanes' sums meet in a fixed order, so a pair's
+// result does not depend on its tile mates.
+constexpr int MV_ROWS = 4, MV_FEAT = 4, MV_WARPS = 8, MV_KC = 1024, MV_IT = MV_KC / 256;
 
 template <typename TO>
-__global__ void __launch_bounds__(MV_WARPS * 32)
+__global__ void __launch_bounds__(MV_WARPS * 32, 2)
 moe_gemv_kernel(const __nv_bfloat16* A, int64_t lda, int a_div, const __nv_bfloat16* __restrict__ Wt, const int* order,
                 const int* plan, TO* out, int N, int K, int act) {
   __shared__ int rows[MV_ROWS];
+  __shared__ uint4 xs[MV_ROWS][MV_KC / 8];
   pdl_wait();
   pdl_trigger();
   const int tile = blockIdx.x;
@@ -293,38 +309,55 @@ moe_gemv_kernel(const __nv_bfloat16* A, int64_t lda, int a_div, const __nv_bfloa
   __syncthreads();
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int n0 = (blockIdx.y * MV_WARPS + warp) * MV_FEAT;
-  if (n0 >= N) return;
   const __nv_bfloat16* Wexp = Wt + (int64_t)e * N * K;
   float acc[MV_FEAT][MV_ROWS];
 #pragma unroll
   for (int f = 0; f < MV_FEAT; ++f)
 #pragma unroll
     for (int r = 0; r < MV_ROWS; ++r) acc[f][r] = 0.0f;
-  for (int k = lane * 8; k < K; k += 256) {
-    uint4 wv[MV_FEAT];
+  for (int k0 = 0; k0 < K; k0 += MV_KC) {
+    // this warp's pieces of W first: they come from DRAM
+    uint4 wv[MV_FEAT][MV_IT];
 #pragma unroll
     for (int f = 0; f < MV_FEAT; ++f) {
       const int n = min(n0 + f, N - 1);
-      wv[f] = __ldg(reinterpret_cast<const uint4*>(Wexp + (int64_t)n * K + k));
+#pragma unroll
+      for (int it = 0; it < MV_IT; ++it) {
+        const int k = k0 + it * 256 + lane * 8;
+        wv[f][it] = k < K ? __ldg(reinterpret_cast<const uint4*>(Wexp + (int64_t)n * K + k)) : make_uint4(0, 0, 0, 0);
+      }
     }
+    for (int i = threadIdx.x; i < MV_ROWS * (MV_KC / 8); i += MV_WARPS * 32) {
+      const int r = i / (MV_KC / 8), c = i - r * (MV_KC / 8);
+      const int p = rows[r], k = k0 + c * 8;
+      xs[r][c] = (p >= 0 && k < K) ? __ldcg(reinterpret_cast<const uint4*>(A + (int64_t)(p / a_div) * lda + k))
+                                   : make_uint4(0, 0, 0, 0);
+    }
+    __syncthreads();
+    if (n0 < N) {
 #pragma unroll
-    for (int r = 0; r < MV_ROWS; ++r) {
-      const int p = rows[r];
-      if (p < 0) continue;
-      const uint4 xv = __ldcg(reinterpret_cast<const uint4*>(A + (int64_t)(p / a_div) * lda + k));
-      const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
+      for (int it = 0; it < MV_IT; ++it) {
 #pragma unroll
-      for (int f = 0; f < MV_FEAT; ++f) {
-        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[f]);
+        for (int r = 0; r < MV_ROWS; ++r) {
+          if (r >= nrows) continue;
+          const uint4 xv = xs[r][it * 32 + lane];
+          const __nv_bfloat162* xp = reinterpret_cast<const __nv_bfloat162*>(&xv);
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float2 a = __bfloat1622float2(xp[j]), b = __bfloat1622float2(wp[j]);
-          acc[f][r] = fmaf(a.x, b.x, acc[f][r]);
-          acc[f][r] = fmaf(a.y, b.y, acc[f][r]);
+          for (int f = 0; f < MV_FEAT; ++f) {
+            const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wv[f][it]);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float2 a = __bfloat1622float2(xp[j]), b = __bfloat1622float2(wp[j]);
+              acc[f][r] = fmaf(a.x, b.x, acc[f][r]);
+              acc[f][r] = fmaf(a.y, b.y, acc[f][r]);
+            }
+          }
         }
       }
     }
+    __syncthreads();
   }
+  if (n0 >= N) return;
 #pragma unroll
   for (int f = 0; f < MV_FEAT; ++f)
 #pragma unroll
@@ -349,29 +382,52 @@ moe_gather_kernel(const __nv_bfloat16* x, int64_t ldx, int top, const int* order
   for (int c = threadIdx.x; c < K / 8; c += blockDim.x) dst[c] = __ldcg(src + c);
 }
 
-template <typename TX>
+// VEC columns a thread (4: H a multiple of 4, float4 loads of y and stores of out).
+template <typename TX, int VEC>
 __global__ void __launch_bounds__(256)
 moe_combine_kernel(const float* y, const int* idx, const float* wt, const TX* x, int64_t ldx, const void* shared,
                    int shared_dtype, const float* gate, float* out, int T, int H, int top, int n_experts) {
   pdl_wait();
   pdl_trigger();
-  const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
   if (i >= (int64_t)T * H) return;
   const int t = (int)(i / H), col = (int)(i - (int64_t)t * H);
-  float acc = 0.0f;
+  float acc[VEC];
+#pragma unroll
+  for (int j = 0; j < VEC; ++j) acc[j] = 0.0f;
   for (int k = 0; k < top; ++k) {
     const int e = __ldcg(idx + (int64_t)t * top + k);
     if (e < 0) continue;
     const float w = __ldcg(wt + (int64_t)t * top + k);
-    const float v = e >= n_experts ? moe_ld(x + (int64_t)t * ldx + col) : __ldcg(y + ((int64_t)t * top + k) * H + col);
-    acc = fmaf(w, v, acc);
+    float v[VEC];
+    if (e >= n_experts) {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) v[j] = moe_ld(x + (int64_t)t * ldx + col + j);
+    } else if (VEC == 4) {
+      const float4 f = __ldcg(reinterpret_cast<const float4*>(y + ((int64_t)t * top + k) * H + col));
+      v[0] = f.x; v[VEC > 1 ? 1 : 0] = f.y; v[VEC > 2 ? 2 : 0] = f.z; v[VEC > 3 ? 3 : 0] = f.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < VEC; ++j) v[j] = __ldcg(y + ((int64_t)t * top + k) * H + col + j);
+    }
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) acc[j] = fmaf(w, v[j], acc[j]);
   }
   if (shared) {
-    const float s = shared_dtype == DT_F32 ? __ldcg(static_cast<const float*>(shared) + i)
-                                           : __bfloat162float(__ldcg(static_cast<const __nv_bfloat16*>(shared) + i));
-    acc = gate ? fmaf(__ldcg(gate + t), s, acc) : acc + s;
+    const float g = gate ? __ldcg(gate + t) : 1.0f;
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) {
+      const float s = shared_dtype == DT_F32 ? __ldcg(static_cast<const float*>(shared) + i + j)
+                                             : __bfloat162float(__ldcg(static_cast<const __nv_bfloat16*>(shared) + i + j));
+      acc[j] = gate ? fmaf(g, s, acc[j]) : acc[j] + s;
+    }
   }
-  out[i] = acc;
+  if (VEC == 4) {
+    *reinterpret_cast<float4*>(out + i) = make_float4(acc[0], acc[VEC > 1 ? 1 : 0], acc[VEC > 2 ? 2 : 0], acc[VEC > 3 ? 3 : 0]);
+  } else {
+#pragma unroll
+    for (int j = 0; j < VEC; ++j) out[i + j] = acc[j];
+  }
 }
 
 }  // namespace exl3
@@ -389,12 +445,15 @@ extern "C" int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const flo
     set_error("moe_route: bad sizes T=%d width=%d outputs=%d groups=%d keep=%d top=%d", T, W, E, groups, keep, top);
     return ERR_BAD_ARGUMENT;
   }
-  const size_t smem = (size_t)RT_TOK * (RT_KC + (E + extra) + E + 2 * groups) * sizeof(float);
+  // all columns staged at once when that takes 64 KB at most, else 4,096 at a time
+  const int stage_cols = W <= 4096 ? ceil_div(W, RT_KC) * RT_KC : 4096;
+  const int pieces = stage_cols / RT_KC;
+  const size_t smem = (size_t)RT_TOK * (stage_cols + (pieces + 1) * (E + extra) + E + 2 * groups) * sizeof(float);
   if (smem > 200 * 1024) { set_error("moe_route: %d router outputs are too many", E); return ERR_UNSUPPORTED; }
-  void (*kernel)(const float*, int64_t, const float*, const float*, int, int, int, int, int, int, int, float, int, int*,
-                 float*, float*) = moe_route_kernel<float>;
+  void (*kernel)(const float*, int64_t, const float*, const float*, int, int, int, int, int, int, int, float, int, int,
+                 int*, float*, float*) = moe_route_kernel<float>;
   void (*kernel_h)(const __nv_bfloat16*, int64_t, const float*, const float*, int, int, int, int, int, int, int, float,
-                   int, int*, float*, float*) = moe_route_kernel<__nv_bfloat16>;
+                   int, int, int*, float*, float*) = moe_route_kernel<__nv_bfloat16>;
   if (smem > 48 * 1024) {
     cudaError_t e = x_dtype == DT_F32
                         ? cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
@@ -404,10 +463,10 @@ extern "C" int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const flo
   const dim3 grid(ceil_div(T, RT_TOK)), threads(RT_WARPS * 32);
   if (x_dtype == DT_F32)
     launch_pdl(kernel, grid, threads, smem, stream, static_cast<const float*>(x), ldx, wr, corr, T, W, E, extra, groups,
-               keep, top, scale, score_kind, idx, wt, gate_out);
+               keep, top, scale, score_kind, stage_cols, idx, wt, gate_out);
   else if (x_dtype == DT_BF16)
     launch_pdl(kernel_h, grid, threads, smem, stream, static_cast<const __nv_bfloat16*>(x), ldx, wr, corr, T, W, E, extra,
-               groups, keep, top, scale, score_kind, idx, wt, gate_out);
+               groups, keep, top, scale, score_kind, stage_cols, idx, wt, gate_out);
   else { set_error("moe_route: unsupported element type %d", x_dtype); return ERR_UNSUPPORTED; }
   return launch_status("moe_route");
 }
@@ -501,14 +560,15 @@ extern "C" int exl3_moe_combine(const float* y, const int* idx, const float* wt,
                                 int top, int n_experts, cudaStream_t stream) {
   if (T == 0) return 0;
   if (T < 0 || H < 1 || top < 1) { set_error("moe_combine: bad sizes"); return ERR_BAD_ARGUMENT; }
-  const int64_t blocks = ((int64_t)T * H + 255) / 256;
+  const bool vec = H % 4 == 0 && (y == nullptr || aligned16(y)) && aligned16(out);
+  const int64_t blocks = ((int64_t)T * H / (vec ? 4 : 1) + 255) / 256;
   if (blocks > 0x7fffffffLL) { set_error("moe_combine: too many elements"); return ERR_UNSUPPORTED; }
-  if (x_dtype == DT_F32)
-    launch_pdl(moe_combine_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, stream, y, idx, wt,
-               static_cast<const float*>(x), ldx, shared, shared_dtype, gate, out, T, H, top, n_experts);
-  else if (x_dtype == DT_BF16)
-    launch_pdl(moe_combine_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(256), 0, stream, y, idx, wt,
-               static_cast<const __nv_bfloat16*>(x), ldx, shared, shared_dtype, gate, out, T, H, top, n_experts);
-  else { set_error("moe_combine: unsupported element type %d", x_dtype); return ERR_UNSUPPORTED; }
+  if (x_dtype != DT_F32 && x_dtype != DT_BF16) { set_error("moe_combine: unsupported element type %d", x_dtype); return ERR_UNSUPPORTED; }
+#define EXL3_COMBINE(TX, VEC)                                                                                        \
+  launch_pdl(moe_combine_kernel<TX, VEC>, dim3((unsigned)blocks), dim3(256), 0, stream, y, idx, wt,                  \
+             static_cast<const TX*>(x), ldx, shared, shared_dtype, gate, out, T, H, top, n_experts)
+  if (x_dtype == DT_F32) { if (vec) EXL3_COMBINE(float, 4); else EXL3_COMBINE(float, 1); }
+  else { if (vec) EXL3_COMBINE(__nv_bfloat16, 4); else EXL3_COMBINE(__nv_bfloat16, 1); }
+#undef EXL3_COMBINE
   return launch_status("moe_combine");
 }

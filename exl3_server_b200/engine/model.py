@@ -123,10 +123,16 @@ class Model:
             return None
         return self.head.forward(stream, self.final_norm, batch.want_rows)
 
-    def weight_bytes(self) -> int:
+    def weight_bytes(self, tokens: Optional[int] = None) -> int:
         """Bytes of weights that one step reads (each matrix once; a tied head
-        reads the embedding table)."""
+        reads the embedding table).  With ``tokens``, routed feed-forwards count the
+        experts that a step of so many tokens is expected to pick; without, all."""
         n = sum(self.blocks[e.layer].weight_bytes() for e in self.plan.schedule)
+        if tokens is not None:
+            for e in self.plan.schedule:
+                ff = getattr(self.blocks[e.layer], "feed_forward", None)
+                if hasattr(ff, "untouched_bytes"):
+                    n -= ff.untouched_bytes(tokens)
         n += self.final_norm.weight_bytes()
         n += self.head.read_bytes()
         return n

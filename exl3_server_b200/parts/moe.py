@@ -119,6 +119,15 @@ class RoutedFeedForward:
         mid = K.moe_gemm(x, self.top, self.w_up, order, plan, self.dtype, act=self.act)
         return K.moe_gemm(mid, 1, self.w_down, order, plan, torch.float32)
 
+    def untouched_bytes(self, tokens: int) -> int:
+        """Bytes of experts' matrices that a step of ``tokens`` tokens is not expected to read when every router output
+        is as likely a pick as any other (random weights): an output stays unpicked by a token with probability
+        ``1 - top / outputs``."""
+        if self.w_up is None:
+            return 0
+        per_expert = (self.w_up[0].numel() + self.w_down[0].numel()) * self.w_up.element_size()
+        return int(self.E * per_expert * (1.0 - self.top / (self.E + self.I)) ** tokens)
+
     def weight_bytes(self) -> int:
         """Weight bytes a token's step reads at most: the router, the shared expert and ``top`` experts per token
         (a step of many tokens reads each expert once; this counts the matrices once)."""
