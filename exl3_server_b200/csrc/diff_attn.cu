@@ -91,26 +91,37 @@ maps_prep_kernel(const void* x, int x_dtype, int64_t ld, int q_off, int k_off, i
   }
 }
 
-// The same for bfloat16 throughout with every size a multiple of 8 (d, rot / 2, dv, the rows, the offsets, the row
-// pitch): a thread takes 8 neighbouring outputs with 16-byte loads and stores.
-__device__ inline void mp_rot8(const __nv_bfloat16* src, int i, int rot, const float* sn, const float* cs, float (&v)[8]) {
-  load_vec_cg(src + i, v);
+// The same for bfloat16 queries and cache (the projection bfloat16 or float32) with every size a multiple of 8 (d,
+// rot / 2, dv, the rows, the offsets, the row pitch): a thread takes 8 neighbouring outputs with 16-byte loads and stores.
+__device__ inline void mp_ld8(const __nv_bfloat16* p, float (&v)[8]) { load_vec_cg(p, v); }
+__device__ inline void mp_ld8(const float* p, float (&v)[8]) {
+  float a[4], b[4];
+  load_vec_cg(p, a);
+  load_vec_cg(p + 4, b);
+#pragma unroll
+  for (int j = 0; j < 4; ++j) { v[j] = a[j]; v[4 + j] = b[j]; }
+}
+
+template <typename TX>
+__device__ inline void mp_rot8(const TX* src, int i, int rot, const float* sn, const float* cs, float (&v)[8]) {
+  mp_ld8(src + i, v);
   if (i >= rot) return;
   const int half = rot >> 1;
   float o[8];
   if (i < half) {
-    load_vec_cg(src + i + half, o);
+    mp_ld8(src + i + half, o);
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = v[j] * cs[i + j] - o[j] * sn[i + j];
   } else {
-    load_vec_cg(src + i - half, o);
+    mp_ld8(src + i - half, o);
 #pragma unroll
     for (int j = 0; j < 8; ++j) v[j] = v[j] * cs[i - half + j] + o[j] * sn[i - half + j];
   }
 }
 
+template <typename TX>
 __global__ void __launch_bounds__(MP_THREADS)
-maps_prep_vec_kernel(const __nv_bfloat16* x, int64_t ld, int q_off, int k_off, int v_off, int nh, int nkv, int maps, int d,
+maps_prep_vec_kernel(const TX* x, int64_t ld, int q_off, int k_off, int v_off, int nh, int nkv, int maps, int d,
                      int dv, int row, int v_row, int rot, const float* __restrict__ f_hi, const float* __restrict__ f_lo,
                      const int* tok_pos, const int* tok_seq, const int* block_table, int bt_stride, int page,
                      __nv_bfloat16* q_out, __nv_bfloat16* k_pool, __nv_bfloat16* v_pool) {
@@ -124,7 +135,7 @@ maps_prep_vec_kernel(const __nv_bfloat16* x, int64_t ld, int q_off, int k_off, i
   float* cs = sc + half;
   for (int i = threadIdx.x; i < half; i += blockDim.x) rope_sincos((float)pos, f_hi[i], f_lo[i], sn + i, cs + i);
   __syncthreads();
-  const __nv_bfloat16* xt = x + (int64_t)t * ld;
+  const TX* xt = x + (int64_t)t * ld;
   const int nq = nh * maps;
   const int n_q = nq * row, n_k = nkv * row, n_v = nkv * v_row;
   const int pg = __ldcg(block_table + (int64_t)__ldcg(tok_seq + t) * bt_stride + pos / page);
@@ -151,7 +162,7 @@ maps_prep_vec_kernel(const __nv_bfloat16* x, int64_t ld, int q_off, int k_off, i
     } else {
       const int idx = item - n_q - n_k;
       const int g = idx / v_row, c = idx - g * v_row;
-      if (c < dv) load_vec_cg(xt + v_off + (int64_t)g * dv + c, v);
+      if (c < dv) mp_ld8(xt + v_off + (int64_t)g * dv + c, v);
       store_vec(v_pool + (((int64_t)pg * nkv + g) * page + slot) * v_row + c, v);
     }
   }
@@ -202,14 +213,21 @@ extern "C" int exl3_maps_prep(const void* x, int x_dtype, int64_t ld, int q_off,
   }
   const int items = nh * maps * row + nkv * row + nkv * v_row;
   if (ceil_div(items, MP_ITEMS) > 65535) { set_error("maps_prep: rows too wide"); return ERR_UNSUPPORTED; }
-  const bool vec = x_dtype == DT_BF16 && q_dtype == DT_BF16 && pool_dtype == DT_BF16 && d % 8 == 0 && (rot >> 1) % 8 == 0 &&
+  const bool vec = (x_dtype == DT_BF16 || x_dtype == DT_F32) && q_dtype == DT_BF16 && pool_dtype == DT_BF16 && d % 8 == 0 && (rot >> 1) % 8 == 0 &&
                    dv % 8 == 0 && row % 8 == 0 && v_row % 8 == 0 && q_off % 8 == 0 && k_off % 8 == 0 && v_off % 8 == 0 &&
                    ld % 8 == 0 && aligned16(x) && aligned16(q_out) && aligned16(k_pool) && aligned16(v_pool);
+  if (vec && x_dtype == DT_BF16) {
+    launch_pdl(maps_prep_vec_kernel<__nv_bfloat16>, dim3(T, ceil_div(items, MP_ITEMS)), dim3(MP_THREADS),
+               (size_t)rot * sizeof(float), stream, static_cast<const __nv_bfloat16*>(x), ld, q_off, k_off, v_off, nh, nkv,
+               maps, d, dv, row, v_row, rot, f_hi, f_lo, tok_pos, tok_seq, block_table, bt_stride, page,
+               static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool));
+    return launch_status("maps_prep");
+  }
   if (vec) {
-    launch_pdl(maps_prep_vec_kernel, dim3(T, ceil_div(items, MP_ITEMS)), dim3(MP_THREADS), (size_t)rot * sizeof(float),
-               stream, static_cast<const __nv_bfloat16*>(x), ld, q_off, k_off, v_off, nh, nkv, maps, d, dv, row, v_row, rot,
-               f_hi, f_lo, tok_pos, tok_seq, block_table, bt_stride, page, static_cast<__nv_bfloat16*>(q_out),
-               static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool));
+    launch_pdl(maps_prep_vec_kernel<float>, dim3(T, ceil_div(items, MP_ITEMS)), dim3(MP_THREADS),
+               (size_t)rot * sizeof(float), stream, static_cast<const float*>(x), ld, q_off, k_off, v_off, nh, nkv, maps, d,
+               dv, row, v_row, rot, f_hi, f_lo, tok_pos, tok_seq, block_table, bt_stride, page,
+               static_cast<__nv_bfloat16*>(q_out), static_cast<__nv_bfloat16*>(k_pool), static_cast<__nv_bfloat16*>(v_pool));
     return launch_status("maps_prep");
   }
   launch_pdl(maps_prep_kernel, dim3(T, ceil_div(items, MP_ITEMS)), dim3(MP_THREADS), (size_t)rot * sizeof(float), stream,

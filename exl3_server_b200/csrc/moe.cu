@@ -22,7 +22,7 @@ namespace exl3 {
 
 constexpr int RT_TOK = 4;        // tokens a block of the router takes (one a warp for the choice)
 constexpr int RT_WARPS = 16;     // warps of a block: router outputs go round over them
-constexpr int RT_KC = 512;       // columns of a piece: what a warp reads of a router row at a time
+constexpr int RT_KC = 512;       // columns of x staged at a time
 constexpr int MOE_TM = 32;       // rows of a tile
 constexpr int MOE_TN = 64;       // output features of a block
 constexpr int MOE_TK = 32;
@@ -48,14 +48,12 @@ __device__ inline void warp_argmax(float& v, int& i) {
 template <typename TX>
 __global__ void __launch_bounds__(RT_WARPS * 32)
 moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const float* __restrict__ corr, int T, int W,
-                 int E, int S, int groups, int keep, int top, float scale, int score_kind, int stage_cols, int* idx,
-                 float* wt, float* gate_out) {
+                 int E, int S, int groups, int keep, int top, float scale, int score_kind, int* idx, float* wt,
+                 float* gate_out) {
   extern __shared__ float rs[];
   const int R = E + S;
-  const int pieces = (stage_cols + RT_KC - 1) / RT_KC;   // pieces of RT_KC columns in what is staged at a time
-  float* xs = rs;                                  // [RT_TOK][stage_cols]
-  float* zp = xs + RT_TOK * stage_cols;            // [pieces][RT_TOK][R]  partial sums of the staged columns
-  float* z = zp + pieces * RT_TOK * R;             // [RT_TOK][R]   logits, then scores
+  float* xs = rs;                                  // [RT_TOK][RT_KC]
+  float* z = xs + RT_TOK * RT_KC;                  // [RT_TOK][R]   logits, then scores
   float* c = z + RT_TOK * R;                       // [RT_TOK][E]   choice scores
   float* gs = c + RT_TOK * E;                      // [RT_TOK][groups] group scores
   float* gk = gs + RT_TOK * groups;                // [RT_TOK][groups] 1: the group is kept
@@ -64,44 +62,33 @@ moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const f
   const int t0 = blockIdx.x * RT_TOK;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   for (int i = threadIdx.x; i < RT_TOK * R; i += blockDim.x) z[i] = 0.0f;
-  // Columns are staged stage_cols at a time (all of them when they fit); a warp takes (output, piece) pairs, so that
-  // the pieces of a row are read side by side; the pieces' sums are added in their order.
-  for (int k0 = 0; k0 < W; k0 += stage_cols) {
-    const int kc = min(stage_cols, W - k0);
+  for (int k0 = 0; k0 < W; k0 += RT_KC) {
+    const int kc = min(RT_KC, W - k0);
     __syncthreads();
-    for (int i = threadIdx.x; i < RT_TOK * stage_cols; i += blockDim.x) {
-      const int tok = i / stage_cols, col = i - tok * stage_cols;
+    for (int i = threadIdx.x; i < RT_TOK * RT_KC; i += blockDim.x) {
+      const int tok = i / RT_KC, col = i - tok * RT_KC;
       xs[i] = (t0 + tok < T && col < kc) ? moe_ld(x + (int64_t)(t0 + tok) * ldx + k0 + col) : 0.0f;
     }
     __syncthreads();
-    for (int item = warp; item < R * pieces; item += RT_WARPS) {
-      const int e = item / pieces, pc = item - e * pieces;
-      const int c0 = pc * RT_KC;
-      const float* wrow = wr + (int64_t)e * W + k0 + c0;
+    for (int e = warp; e < R; e += RT_WARPS) {
+      const float* wrow = wr + (int64_t)e * W + k0;
       float part[RT_TOK];
 #pragma unroll
       for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = 0.0f;
-      // a fixed number of rounds, so that the piece's loads are all under way before the first is used
+      // a fixed number of rounds, so that the row's loads are all under way before the first is used
       float wv[RT_KC / 32];
 #pragma unroll
-      for (int i = 0; i < RT_KC / 32; ++i) wv[i] = c0 + lane + 32 * i < kc ? wrow[lane + 32 * i] : 0.0f;
+      for (int i = 0; i < RT_KC / 32; ++i) wv[i] = lane + 32 * i < kc ? wrow[lane + 32 * i] : 0.0f;
 #pragma unroll
       for (int i = 0; i < RT_KC / 32; ++i) {
-        const int col = min(c0 + lane + 32 * i, stage_cols - 1);
 #pragma unroll
-        for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = fmaf(wv[i], xs[tok * stage_cols + col], part[tok]);
+        for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = fmaf(wv[i], xs[tok * RT_KC + lane + 32 * i], part[tok]);
       }
 #pragma unroll
       for (int tok = 0; tok < RT_TOK; ++tok) {
         const float s = warp_sum(part[tok]);
-        if (lane == 0) zp[(pc * RT_TOK + tok) * R + e] = s;
+        if (lane == 0) z[tok * R + e] += s;
       }
-    }
-    __syncthreads();
-    for (int i = threadIdx.x; i < RT_TOK * R; i += blockDim.x) {
-      float s = z[i];
-      for (int pc = 0; pc < pieces; ++pc) s += zp[pc * RT_TOK * R + i];
-      z[i] = s;
     }
   }
   __syncthreads();
@@ -445,15 +432,12 @@ extern "C" int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const flo
     set_error("moe_route: bad sizes T=%d width=%d outputs=%d groups=%d keep=%d top=%d", T, W, E, groups, keep, top);
     return ERR_BAD_ARGUMENT;
   }
-  // all columns staged at once when that takes 64 KB at most, else 4,096 at a time
-  const int stage_cols = W <= 4096 ? ceil_div(W, RT_KC) * RT_KC : 4096;
-  const int pieces = stage_cols / RT_KC;
-  const size_t smem = (size_t)RT_TOK * (stage_cols + (pieces + 1) * (E + extra) + E + 2 * groups) * sizeof(float);
+  const size_t smem = (size_t)RT_TOK * (RT_KC + (E + extra) + E + 2 * groups) * sizeof(float);
   if (smem > 200 * 1024) { set_error("moe_route: %d router outputs are too many", E); return ERR_UNSUPPORTED; }
-  void (*kernel)(const float*, int64_t, const float*, const float*, int, int, int, int, int, int, int, float, int, int,
-                 int*, float*, float*) = moe_route_kernel<float>;
+  void (*kernel)(const float*, int64_t, const float*, const float*, int, int, int, int, int, int, int, float, int, int*,
+                 float*, float*) = moe_route_kernel<float>;
   void (*kernel_h)(const __nv_bfloat16*, int64_t, const float*, const float*, int, int, int, int, int, int, int, float,
-                   int, int, int*, float*, float*) = moe_route_kernel<__nv_bfloat16>;
+                   int, int*, float*, float*) = moe_route_kernel<__nv_bfloat16>;
   if (smem > 48 * 1024) {
     cudaError_t e = x_dtype == DT_F32
                         ? cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)
@@ -463,10 +447,10 @@ extern "C" int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const flo
   const dim3 grid(ceil_div(T, RT_TOK)), threads(RT_WARPS * 32);
   if (x_dtype == DT_F32)
     launch_pdl(kernel, grid, threads, smem, stream, static_cast<const float*>(x), ldx, wr, corr, T, W, E, extra, groups,
-               keep, top, scale, score_kind, stage_cols, idx, wt, gate_out);
+               keep, top, scale, score_kind, idx, wt, gate_out);
   else if (x_dtype == DT_BF16)
     launch_pdl(kernel_h, grid, threads, smem, stream, static_cast<const __nv_bfloat16*>(x), ldx, wr, corr, T, W, E, extra,
-               groups, keep, top, scale, score_kind, stage_cols, idx, wt, gate_out);
+               groups, keep, top, scale, score_kind, idx, wt, gate_out);
   else { set_error("moe_route: unsupported element type %d", x_dtype); return ERR_UNSUPPORTED; }
   return launch_status("moe_route");
 }

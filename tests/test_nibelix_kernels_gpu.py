@@ -292,11 +292,14 @@ def test_scan_with_silu_inputs(dt):
     assert torch.equal(state[1].double().cpu(), before[1])          # a slot of no row stays as it was
 
 
-@pytest.mark.parametrize("dt", TYPES)
-@pytest.mark.parametrize("H, G, d, dv, rot", [(4, 2, 24, 16, 12), (3, 3, 10, 6, 10), (2, 1, 64, 128, 0), (8, 2, 32, 64, 32)])
-def test_maps_prep(dt, H, G, d, dv, rot):
+@pytest.mark.parametrize("dt, x_dt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                      (torch.bfloat16, torch.float32)])
+@pytest.mark.parametrize("H, G, d, dv, rot", [(4, 2, 24, 16, 12), (3, 3, 10, 6, 10), (2, 1, 64, 128, 0), (8, 2, 32, 64, 32),
+                                              (4, 4, 64, 128, 32)])
+def test_maps_prep(dt, x_dt, H, G, d, dv, rot):
     """Rotation of part of every map, the queries widened to a head per map, keys and values at their places in the
-    pages (two sequences, the second starting in the middle of a page)."""
+    pages (two sequences, the second starting in the middle of a page); the projection in the queries' type or in
+    float32 (as steps of few tokens leave it)."""
     g = torch.Generator().manual_seed(H * d)
     row, v_row, page = (2 * d + 7) // 8 * 8, (dv + 7) // 8 * 8, 16
     seqs = [(0, 0, 5), (1, 29, 6)]                            # (sequence, first position, tokens)
@@ -305,7 +308,7 @@ def test_maps_prep(dt, H, G, d, dv, rot):
     T = len(tok_pos)
     block_table = torch.tensor([[3, 1, -1], [0, 4, 2]], dtype=torch.int32, device=DEV)
     ld = H * 2 * d + G * 2 * d + G * dv + 8
-    x = torch.randn(T, ld, generator=g).to(dt).to(DEV)
+    x = torch.randn(T, ld, generator=g).to(x_dt).to(DEV)
     k_pool = torch.zeros(5, G, page, row, dtype=dt, device=DEV)
     v_pool = torch.zeros(5, G, page, v_row, dtype=dt, device=DEV)
     inv = torch.tensor([300.0 ** (-2.0 * i / rot) for i in range(rot // 2)], dtype=torch.float64) if rot else None
