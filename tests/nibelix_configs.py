@@ -74,6 +74,13 @@ CONFIGS = {
         L("lightning", light(2, 128, 64, (0.99, 0.9)), moe(96, 8, 0, 2, 1.0, groups=(2, 1))),
         L("attention", attn(4, 2, 32, 64, 0.18, 0.1, window=100), dense(192)),
     ]),
+    # key rows of 64 features, the tensor-core attention kernels' other shape: values narrower than the row (padded), a
+    # window shorter than a page, one kv head for 4 and for 12 query heads (24 maps on a kv head: more than the decode
+    # kernel takes, so decoding falls to the CUDA-core kernel while prompts stay on the tensor cores), no window
+    "tensor": NibelixConfig(vocab=160, width=128, norm_eps=1e-6, residual_mult=0.6, logit_softcap=15.0, layers=[
+        L("attention", attn(4, 1, 32, 48, 0.18, 0.3, window=20), dense(96)),
+        L("attention", attn(12, 1, 32, 64, 0.18, 0.2, dims=16), moe(24, 4, 1, 2, 1.2, shared=32)),
+    ]),
     # one mechanism alone (the smallest feed-forward there can be where the mechanism is a mixer)
     "only_attention": NibelixConfig(vocab=128, width=80, norm_eps=1e-6, residual_mult=0.5, logit_softcap=20.0, layers=[
         L("attention", attn(4, 2, 32, 24, 0.18, 0.3, window=70, dims=16), None)]),
@@ -88,6 +95,46 @@ CONFIGS = {
     "only_routed": NibelixConfig(vocab=128, width=80, norm_eps=1e-6, residual_mult=0.5, logit_softcap=20.0, layers=[
         L("lightning", light(1, 8, 8, (0.5,)), moe(48, 10, 2, 3, 1.7, groups=(3, 2), shared=40))]),
 }
+
+def random_config(seed: int) -> NibelixConfig:
+    """A configuration drawn from a seed: two to five layers of either kind in any order, every size, count and constant
+    drawn anew (within what the design allows), a dense, routed or no feed-forward beside each."""
+    import random
+    r = random.Random(seed)
+    width = r.choice([48, 72, 80, 104, 136])
+    layers = []
+    for _ in range(r.randint(2, 5)):
+        if r.random() < 0.5:
+            heads = r.randint(1, 4)
+            mixer = light(heads, r.choice([4, 8, 12, 16, 32, 40]), r.choice([6, 8, 16, 24, 32]),
+                          [r.choice([1.0, 0.999, 0.97, 0.9, 0.6, 0.3]) for _ in range(heads)])
+            kind = "lightning"
+        else:
+            kv = r.randint(1, 3)
+            dim = r.choice([6, 8, 16, 24, 32, 64])
+            mixer = attn(kv * r.randint(1, 4), kv, dim, r.choice([8, 12, 16, 32, 64, 128]), r.uniform(0.1, 0.3),
+                         r.uniform(0.05, 0.7), window=r.choice([None, 1, 2, 5, 31, 64, 65, 200]),
+                         base=r.choice([100.0, 10000.0, 1e6]), dims=r.choice([0, 2, dim // 2 * 2, dim]))
+            kind = "attention"
+        what = r.random()
+        if what < 0.25:
+            mlp = None
+        elif what < 0.5:
+            mlp = dense(r.choice([24, 40, 100]))
+        else:
+            per, groups = r.randint(1, 4), r.randint(1, 4)
+            n = per * groups
+            identity = r.randint(0, min(2, n - 1)) if n > 1 else 0
+            keep = r.randint(1, groups)
+            mlp = moe(r.choice([8, 24, 40]), n - identity, identity, r.randint(1, keep * per), r.uniform(0.5, 2.5),
+                      groups=(groups, keep), shared=r.choice([None, 16, 40]))
+        layers.append(L(kind, mixer, mlp))
+    return NibelixConfig(vocab=r.randint(40, 300), width=width, norm_eps=r.choice([1e-6, 1e-5, 1e-4]),
+                         residual_mult=r.uniform(0.3, 1.0), logit_softcap=r.choice([0.0, 10.0, 30.0, 50.0]), layers=layers)
+
+
+RANDOM_SEEDS = list(range(100, 112))
+CONFIGS.update({f"random{seed}": random_config(seed) for seed in RANDOM_SEEDS})
 
 ROUTED = {name for name, c in CONFIGS.items() if any(l.mlp and l.mlp["kind"] == "moe" for l in c.layers)}
 

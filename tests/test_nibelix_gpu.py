@@ -26,7 +26,8 @@ from plain_nibelix import PlainNibelix
 pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DTYPES = ["float32", "bfloat16"]
-LENGTHS = {"mixed": [1, 2, 9, 64, 65, 150], "odd": [1, 3, 20, 64, 66, 131], "wide": [3, 17, 63, 128, 129, 300]}
+LENGTHS = {"mixed": [1, 2, 9, 64, 65, 150], "odd": [1, 3, 20, 64, 66, 131], "wide": [3, 17, 63, 128, 129, 300],
+           "tensor": [1, 2, 19, 21, 130, 330]}
 ONLY_LENGTHS = [1, 2, 31, 64, 129, 140]
 FLIP_SHARE = 0.15         # bfloat16 with routers: positions that may be beyond the bound
 
@@ -88,7 +89,7 @@ def check(got, want, dtype, name, what):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", list(CONFIGS))
+@pytest.mark.parametrize("name", [n for n in CONFIGS if not n.startswith("random")])
 def test_whole_decoded_and_batched(folders, name, dtype):
     folder = folders[name]
     requests = requests_for(name, folder, LENGTHS.get(name, ONLY_LENGTHS), seed=3)
@@ -110,6 +111,25 @@ def test_whole_decoded_and_batched(folders, name, dtype):
     eng.check_kernels()
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", [n for n in CONFIGS if n.startswith("random")])
+def test_configurations_drawn_from_a_seed(folders, name, dtype):
+    """Layer orders, sizes, counts and constants that nobody chose: whole prompts, the last tokens one by one, and
+    a batch of unequal requests decoded together."""
+    folder = folders[name]
+    requests = requests_for(name, folder, [1, 2, 40, 66, 150], seed=41)
+    pm = plain(folder)
+    want = {rid: pm.logits(t).numpy() for rid, t in requests.items()}
+    eng = engine_for(folder, dtype)
+    check(run_trace(eng, whole_trace(requests)), want, dtype, name, "whole")
+    check(run_trace(eng, tail_trace(requests, 70)), want, dtype, name, "last 70 one by one")
+    ids = list(requests)
+    prompt_len = {rid: max(1, len(requests[rid]) - k) for rid, k in zip(ids, (0, 1, 35, 3, 80))}
+    check(run_trace(eng, batched_trace(requests, [ids[::-1]], prompt_len)), want, dtype, name, "batched")
+    assert eng.cache.tokens_held() == 0
+    eng.check_kernels()
+
+
 @pytest.mark.parametrize("name", ["mixed", "wide"])
 def test_float32_cuttings_agree_closely(folders, name):
     requests = requests_for(name, folders[name], LENGTHS[name], seed=5)
@@ -121,7 +141,7 @@ def test_float32_cuttings_agree_closely(folders, name):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["mixed", "odd", "wide"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "wide", "tensor"])
 def test_portions_of_a_prompt(folders, name, dtype):
     """A prompt fed in portions of many sizes, down to two tokens, some ending on a page border, on a window's edge
     and inside one, and one long enough for the recurrence's chunks to run side by side and for the experts to take
@@ -264,7 +284,7 @@ def test_a_token_far_back_in_the_state(folders, tmp_path, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["mixed", "odd", "wide"])
+@pytest.mark.parametrize("name", ["mixed", "odd", "wide", "tensor"])
 def test_long_decoding(folders, name, dtype):
     """Three tokens of prompt, then 200 decoded one by one over three page borders and past every window, two
     sequences side by side."""
