@@ -485,7 +485,7 @@ head_norm_gate_kernel(const float* o, const void* __restrict__ w, int w_dtype, c
 // The same for wide heads (all heads normed together make one of heads * dv values): a block per (token, head), the
 // head's values kept in registers between the sum of squares and the output (up to HN_WIDE_PER values a thread; what is
 // beyond is read again).
-constexpr int HN_WIDE_THREADS = 256, HN_WIDE_PER = 8;
+constexpr int HN_WIDE_THREADS = 512, HN_WIDE_PER = 8;
 
 __global__ void __launch_bounds__(HN_WIDE_THREADS)
 head_norm_gate_wide_kernel(const float* o, const void* __restrict__ w, int w_dtype, const void* gate, int gate_dtype,

@@ -23,6 +23,7 @@ namespace exl3 {
 constexpr int RT_TOK = 4;        // tokens a block of the router takes (one a warp for the choice)
 constexpr int RT_WARPS = 16;     // warps of a block: router outputs go round over them
 constexpr int RT_KC = 512;       // columns of x staged at a time
+constexpr int RT_FEW_TOKENS = 64; // steps of up to so many tokens take the router's few-token form
 constexpr int MOE_TM = 32;       // rows of a tile
 constexpr int MOE_TN = 64;       // output features of a block
 constexpr int MOE_TK = 32;
@@ -45,59 +46,10 @@ __device__ inline void warp_argmax(float& v, int& i) {
   }
 }
 
-template <typename TX>
-__global__ void __launch_bounds__(RT_WARPS * 32)
-moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const float* __restrict__ corr, int T, int W,
-                 int E, int S, int groups, int keep, int top, float scale, int score_kind, int* idx, float* wt,
-                 float* gate_out) {
-  extern __shared__ float rs[];
-  const int R = E + S;
-  float* xs = rs;                                  // [RT_TOK][RT_KC]
-  float* z = xs + RT_TOK * RT_KC;                  // [RT_TOK][R]   logits, then scores
-  float* c = z + RT_TOK * R;                       // [RT_TOK][E]   choice scores
-  float* gs = c + RT_TOK * E;                      // [RT_TOK][groups] group scores
-  float* gk = gs + RT_TOK * groups;                // [RT_TOK][groups] 1: the group is kept
-  pdl_wait();
-  pdl_trigger();
-  const int t0 = blockIdx.x * RT_TOK;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  for (int i = threadIdx.x; i < RT_TOK * R; i += blockDim.x) z[i] = 0.0f;
-  for (int k0 = 0; k0 < W; k0 += RT_KC) {
-    const int kc = min(RT_KC, W - k0);
-    __syncthreads();
-    for (int i = threadIdx.x; i < RT_TOK * RT_KC; i += blockDim.x) {
-      const int tok = i / RT_KC, col = i - tok * RT_KC;
-      xs[i] = (t0 + tok < T && col < kc) ? moe_ld(x + (int64_t)(t0 + tok) * ldx + k0 + col) : 0.0f;
-    }
-    __syncthreads();
-    for (int e = warp; e < R; e += RT_WARPS) {
-      const float* wrow = wr + (int64_t)e * W + k0;
-      float part[RT_TOK];
-#pragma unroll
-      for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = 0.0f;
-      // a fixed number of rounds, so that the row's loads are all under way before the first is used
-      float wv[RT_KC / 32];
-#pragma unroll
-      for (int i = 0; i < RT_KC / 32; ++i) wv[i] = lane + 32 * i < kc ? wrow[lane + 32 * i] : 0.0f;
-#pragma unroll
-      for (int i = 0; i < RT_KC / 32; ++i) {
-#pragma unroll
-        for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = fmaf(wv[i], xs[tok * RT_KC + lane + 32 * i], part[tok]);
-      }
-#pragma unroll
-      for (int tok = 0; tok < RT_TOK; ++tok) {
-        const float s = warp_sum(part[tok]);
-        if (lane == 0) z[tok * R + e] += s;
-      }
-    }
-  }
-  __syncthreads();
-  const int t = t0 + warp;                         // this warp's token
-  if (warp >= RT_TOK || t >= T) return;
-  float* zt = z + warp * R;
-  float* ct = c + warp * E;
-  float* gst = gs + warp * groups;
-  float* gkt = gk + warp * groups;
+// The choice of one token by one warp: zt [E (+ S)] logits (scores on return), ct [E], gst and gkt [groups] scratch.
+__device__ inline void route_choice(int t, int lane, float* zt, float* ct, float* gst, float* gkt,
+                                    const float* __restrict__ corr, int E, int S, int groups, int keep, int top,
+                                    float scale, int score_kind, int* idx, float* wt, float* gate_out) {
   if (S && lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-zt[E]));
   if (score_kind == 0) {
     float mx = -INFINITY;
@@ -163,6 +115,124 @@ moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const f
     }
     __syncwarp();
   }
+}
+
+template <typename TX>
+__global__ void __launch_bounds__(RT_WARPS * 32)
+moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const float* __restrict__ corr, int T, int W,
+                 int E, int S, int groups, int keep, int top, float scale, int score_kind, int* idx, float* wt,
+                 float* gate_out) {
+  extern __shared__ float rs[];
+  const int R = E + S;
+  float* xs = rs;                                  // [RT_TOK][RT_KC]
+  float* z = xs + RT_TOK * RT_KC;                  // [RT_TOK][R]   logits, then scores
+  float* c = z + RT_TOK * R;                       // [RT_TOK][E]   choice scores
+  float* gs = c + RT_TOK * E;                      // [RT_TOK][groups] group scores
+  float* gk = gs + RT_TOK * groups;                // [RT_TOK][groups] 1: the group is kept
+  pdl_wait();
+  pdl_trigger();
+  const int t0 = blockIdx.x * RT_TOK;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int i = threadIdx.x; i < RT_TOK * R; i += blockDim.x) z[i] = 0.0f;
+  for (int k0 = 0; k0 < W; k0 += RT_KC) {
+    const int kc = min(RT_KC, W - k0);
+    __syncthreads();
+    for (int i = threadIdx.x; i < RT_TOK * RT_KC; i += blockDim.x) {
+      const int tok = i / RT_KC, col = i - tok * RT_KC;
+      xs[i] = (t0 + tok < T && col < kc) ? moe_ld(x + (int64_t)(t0 + tok) * ldx + k0 + col) : 0.0f;
+    }
+    __syncthreads();
+    for (int e = warp; e < R; e += RT_WARPS) {
+      const float* wrow = wr + (int64_t)e * W + k0;
+      float part[RT_TOK];
+#pragma unroll
+      for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = 0.0f;
+      // a fixed number of rounds, so that the row's loads are all under way before the first is used
+      float wv[RT_KC / 32];
+#pragma unroll
+      for (int i = 0; i < RT_KC / 32; ++i) wv[i] = lane + 32 * i < kc ? wrow[lane + 32 * i] : 0.0f;
+#pragma unroll
+      for (int i = 0; i < RT_KC / 32; ++i) {
+#pragma unroll
+        for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = fmaf(wv[i], xs[tok * RT_KC + lane + 32 * i], part[tok]);
+      }
+#pragma unroll
+      for (int tok = 0; tok < RT_TOK; ++tok) {
+        const float s = warp_sum(part[tok]);
+        if (lane == 0) z[tok * R + e] += s;
+      }
+    }
+  }
+  __syncthreads();
+  const int t = t0 + warp;                         // this warp's token
+  if (warp >= RT_TOK || t >= T) return;
+  float* zt = z + warp * R;
+  float* ct = c + warp * E;
+  float* gst = gs + warp * groups;
+  float* gkt = gk + warp * groups;
+  route_choice(t, lane, zt, ct, gst, gkt, corr, E, S, groups, keep, top, scale, score_kind, idx, wt, gate_out);
+}
+
+// The router for steps of few tokens (decode), where the chain of dependent loads is what costs: a token a block,
+// all of its input in shared memory at once, and the (output, piece of RT_KC columns) pairs spread over 32 warps, each
+// of which has the next pair's piece of the router's row under way while it works on the present one.  The pieces'
+// sums are added in their order, so the logits are those of a fixed order whatever the step holds.
+constexpr int RS_WARPS = 32;
+
+__device__ inline void rs_load(float (&wv)[RT_KC / 32], const float* __restrict__ wr, int W, int pieces, int item, int lane) {
+  const int e = item / pieces, c0 = (item - e * pieces) * RT_KC;
+  const float* wrow = wr + (int64_t)e * W + c0;
+#pragma unroll
+  for (int i = 0; i < RT_KC / 32; ++i) wv[i] = c0 + lane + 32 * i < W ? wrow[lane + 32 * i] : 0.0f;
+}
+
+template <typename TX>
+__global__ void __launch_bounds__(RS_WARPS * 32)
+moe_route_few_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const float* __restrict__ corr, int T, int W,
+                     int E, int S, int groups, int keep, int top, float scale, int score_kind, int* idx, float* wt,
+                     float* gate_out) {
+  extern __shared__ float rs[];
+  const int R = E + S;
+  const int pieces = (W + RT_KC - 1) / RT_KC;
+  const int cols = pieces * RT_KC;
+  float* xs = rs;                                  // [cols], zeros beyond W
+  float* zp = xs + cols;                           // [pieces][R] sums of the pieces
+  float* z = zp + pieces * R;                      // [R] logits, then scores
+  float* c = z + R;                                // [E] choice scores
+  float* gs = c + E;                               // [groups]
+  float* gk = gs + groups;                         // [groups]
+  const int t = blockIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int n_items = R * pieces;
+  // the router's rows do not depend on the kernel before: the first piece is asked for before waiting for it
+  float cur[RT_KC / 32], nxt[RT_KC / 32];
+  if (warp < n_items) rs_load(cur, wr, W, pieces, warp, lane);
+  pdl_wait();
+  pdl_trigger();
+  for (int i = threadIdx.x; i < cols; i += blockDim.x) xs[i] = i < W ? moe_ld(x + (int64_t)t * ldx + i) : 0.0f;
+  __syncthreads();
+  for (int item = warp; item < n_items; item += RS_WARPS) {
+    const bool more = item + RS_WARPS < n_items;
+    if (more) rs_load(nxt, wr, W, pieces, item + RS_WARPS, lane);
+    const int e = item / pieces, pc = item - e * pieces;
+    float part = 0.0f;
+#pragma unroll
+    for (int i = 0; i < RT_KC / 32; ++i) part = fmaf(cur[i], xs[pc * RT_KC + lane + 32 * i], part);
+    part = warp_sum(part);
+    if (lane == 0) zp[pc * R + e] = part;
+    if (more) {
+#pragma unroll
+      for (int i = 0; i < RT_KC / 32; ++i) cur[i] = nxt[i];
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < R; i += blockDim.x) {
+    float sum = 0.0f;
+    for (int pc = 0; pc < pieces; ++pc) sum += zp[pc * R + i];
+    z[i] = sum;
+  }
+  __syncthreads();
+  if (warp == 0) route_choice(t, lane, z, c, gs, gk, corr, E, S, groups, keep, top, scale, score_kind, idx, wt, gate_out);
 }
 
 // One block.  plan[0]: number of tiles; plan[1]: planned pairs (places of `order` in use); then per tile (expert,
@@ -431,6 +501,28 @@ extern "C" int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const flo
       top < 1 || top > keep * (E / groups) || (extra && gate_out == nullptr) || score_kind < 0 || score_kind > 1) {
     set_error("moe_route: bad sizes T=%d width=%d outputs=%d groups=%d keep=%d top=%d", T, W, E, groups, keep, top);
     return ERR_BAD_ARGUMENT;
+  }
+  // few tokens: a block a token with all of its input staged, when that fits
+  const int pieces = ceil_div(W, RT_KC);
+  const size_t smem_few = ((size_t)pieces * RT_KC + (size_t)(pieces + 1) * (E + extra) + E + 2 * groups) * sizeof(float);
+  if (T <= RT_FEW_TOKENS && smem_few <= 160 * 1024 && (x_dtype == DT_F32 || x_dtype == DT_BF16)) {
+    void (*few)(const float*, int64_t, const float*, const float*, int, int, int, int, int, int, int, float, int, int*,
+                float*, float*) = moe_route_few_kernel<float>;
+    void (*few_h)(const __nv_bfloat16*, int64_t, const float*, const float*, int, int, int, int, int, int, int, float,
+                  int, int*, float*, float*) = moe_route_few_kernel<__nv_bfloat16>;
+    if (smem_few > 48 * 1024) {
+      cudaError_t e = x_dtype == DT_F32
+                          ? cudaFuncSetAttribute(few, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_few)
+                          : cudaFuncSetAttribute(few_h, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_few);
+      if (e != cudaSuccess) { set_error("moe_route: shared memory refused: %s", cudaGetErrorString(e)); return (int)e; }
+    }
+    if (x_dtype == DT_F32)
+      launch_pdl(few, dim3(T), dim3(RS_WARPS * 32), smem_few, stream, static_cast<const float*>(x), ldx, wr, corr, T, W, E,
+                 extra, groups, keep, top, scale, score_kind, idx, wt, gate_out);
+    else
+      launch_pdl(few_h, dim3(T), dim3(RS_WARPS * 32), smem_few, stream, static_cast<const __nv_bfloat16*>(x), ldx, wr, corr,
+                 T, W, E, extra, groups, keep, top, scale, score_kind, idx, wt, gate_out);
+    return launch_status("moe_route");
   }
   const size_t smem = (size_t)RT_TOK * (RT_KC + (E + extra) + E + 2 * groups) * sizeof(float);
   if (smem > 200 * 1024) { set_error("moe_route: %d router outputs are too many", E); return ERR_UNSUPPORTED; }

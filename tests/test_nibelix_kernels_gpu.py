@@ -93,7 +93,8 @@ def plain_route(z, corr, groups, keep, top, scale, score):
 @pytest.mark.parametrize("dt", TYPES)
 @pytest.mark.parametrize("T, W, n, groups, keep, top, score, extra", [
     (1, 96, 8, 1, 1, 2, "softmax", 1), (5, 100, 12, 3, 2, 3, "softmax", 0), (37, 2048, 16, 4, 2, 2, "softmax", 1),
-    (9, 520, 40, 8, 3, 6, "sigmoid", 1), (4, 64, 6, 6, 2, 2, "softmax", 0), (3, 72, 5, 1, 1, 5, "softmax", 1)])
+    (9, 520, 40, 8, 3, 6, "sigmoid", 1), (4, 64, 6, 6, 2, 2, "softmax", 0), (3, 72, 5, 1, 1, 5, "softmax", 1),
+    (150, 1100, 12, 2, 1, 2, "softmax", 1), (70, 4096, 18, 3, 2, 4, "softmax", 1), (2, 5000, 9, 1, 1, 3, "softmax", 0)])
 def test_route(dt, T, W, n, groups, keep, top, score, extra):
     g = torch.Generator().manual_seed(T + W + n)
     x = torch.randn(T, W, generator=g).to(dt).to(DEV)
@@ -109,6 +110,10 @@ def test_route(dt, T, W, n, groups, keep, top, score, extra):
         close(gate, torch.sigmoid(z[:, n]), torch.float32)
     else:
         assert gate is None
+    # a token's picks and weights are the same bits whether it comes alone (the few-token form) or among many
+    if T > 64:
+        idx1, wt1, _ = K().moe_route(x[:3], wr, corr, n, extra, groups, keep, top, 1.7, score)
+        assert torch.equal(idx1, idx[:3]) and torch.equal(wt1, wt[:3])
 
 
 def experts_reference(x, idx, w_up, w_down, act):
