@@ -21,7 +21,7 @@
 namespace exl3 {
 
 constexpr int RT_TOK = 4;        // tokens a block of the router takes (one a warp for the choice)
-constexpr int RT_WARPS = 16;     // warps of a block: router outputs go round over them
+constexpr int RT_WARPS = 16;     // warps of a block: router outputs are dealt out to them in turn
 constexpr int RT_KC = 512;       // columns of x staged at a time
 constexpr int RT_FEW_TOKENS = 64; // steps of up to so many tokens take the router's few-token form
 constexpr int MOE_TM = 32;       // rows of a tile
@@ -147,7 +147,7 @@ moe_route_kernel(const TX* x, int64_t ldx, const float* __restrict__ wr, const f
       float part[RT_TOK];
 #pragma unroll
       for (int tok = 0; tok < RT_TOK; ++tok) part[tok] = 0.0f;
-      // a fixed number of rounds, so that the row's loads are all under way before the first is used
+      // a fixed number of passes, so that the row's loads are all under way before the first is used
       float wv[RT_KC / 32];
 #pragma unroll
       for (int i = 0; i < RT_KC / 32; ++i) wv[i] = lane + 32 * i < kc ? wrow[lane + 32 * i] : 0.0f;

@@ -15,7 +15,7 @@
 //   warps 2-5 epilogue: thread = row, 32 accumulator columns at a time from tensor memory, the activation, and
 //             16-byte stores: in the plan's order (the first projection's output, the second one's input) or to the
 //             pair's own place order[i] (float32, for the weighted sum)
-// Two accumulators let the epilogue of one tile overlap the products of the next.  Work items go round the blocks
+// Two accumulators let the epilogue of one tile overlap the products of the next.  Work items are dealt to the blocks in turn
 // with the plan's tile fastest: blocks that run together read the same 256 rows of an expert that has several tiles.
 //
 // Every wait on an mbarrier is bounded: when one runs out the kernel records a code, leaves its loops, waits
