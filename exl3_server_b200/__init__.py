@@ -1,4 +1,4 @@
-"""A small single-GPU generation library for the Llama-family, Rigitar, Nikodra and Nibelix decoders, written for B200 (sm_100a).
+"""A small single-GPU generation library for the Llama-family, Rigitar, Nikodra, Nibelix and Potodra decoders, written for B200 (sm_100a).
 
 Entry points::
 
@@ -7,12 +7,12 @@ Entry points::
     results = generate(engine, prompts=[[1, 2, 3]], options=GenerateOptions(max_tokens=16))
 """
 from . import models  # noqa: F401  (registers the architectures)
-from .config import ConfigError, LlamaConfig, NibelixConfig, NikodraConfig, RigitarConfig, register_architecture, resolve_architecture
+from .config import ConfigError, LlamaConfig, NibelixConfig, NikodraConfig, PotodraConfig, RigitarConfig, register_architecture, resolve_architecture
 from .engine import (Engine, GenerateOptions, GenerateResult, Model, StepEntry, StepError, generate,
                      load_model)
 from .sampling import SampleOptions
 from .weights import WeightsError
 from .weights.random_init import write_random_model
 
-__all__ = ["ConfigError", "LlamaConfig", "RigitarConfig", "NikodraConfig", "NibelixConfig", "register_architecture", "resolve_architecture", "Engine", "Model", "GenerateOptions", "GenerateResult", "SampleOptions", "generate",
+__all__ = ["ConfigError", "LlamaConfig", "RigitarConfig", "NikodraConfig", "NibelixConfig", "PotodraConfig", "register_architecture", "resolve_architecture", "Engine", "Model", "GenerateOptions", "GenerateResult", "SampleOptions", "generate",
            "StepEntry", "StepError", "load_model", "WeightsError", "write_random_model"]

@@ -102,6 +102,11 @@ class KVGroup:
             first = max(first, length // c * c)        # the block of positions that holds ``length``
         return first // self.page_size
 
+    def kept_pages(self) -> int:
+        """Logical pages from the start that are never given back: they hold positions that every later query sees."""
+        k = self.request.keep_first
+        return (k + self.page_size - 1) // self.page_size if k > 0 else 0
+
 
 class SequenceCache:
     """Slots, key/value groups and per-sequence state for one model.
@@ -139,6 +144,9 @@ class SequenceCache:
                         raise CacheError(f"schedule entry {i} cannot read entry {src}'s cache: head shapes differ")
                     # the owner gives back the pages its own window no longer reaches: a reader that looks
                     # further back would find them gone (the kernels skip pages that are not there)
+                    if src_req.window > 0 and kv.keep_first > src_req.keep_first:
+                        raise CacheError(f"schedule entry {i} keeps the first {kv.keep_first} keys, entry {src}'s cache "
+                                         f"only {src_req.keep_first}")
                     if src_req.window > 0 and not 0 < kv.window <= src_req.window:
                         raise CacheError(f"schedule entry {i} (window {kv.window or 'none'}) cannot read entry "
                                          f"{src}'s cache, which keeps only a window of {src_req.window}")
@@ -232,11 +240,12 @@ class SequenceCache:
         any_gone = False
         for g in self.groups:
             first = g.first_needed_page(new_len)
+            kept = g.kept_pages()
             pages = g.pages[slot]
-            gone = [p for p in pages[:first] if p >= 0]
+            gone = [p for p in pages[kept:first] if p >= 0]
             if gone:
                 g.pool.free(gone)
-                for i in range(min(first, len(pages))):
+                for i in range(kept, min(first, len(pages))):
                     pages[i] = -1
                 any_gone = True
         return any_gone
@@ -244,7 +253,8 @@ class SequenceCache:
     def gives_back_at(self, length: int) -> bool:
         """Whether a sequence that has just reached ``length`` has a page to give back that it still needed
         at ``length - 1`` (only groups with a window ever do)."""
-        return any(g.first_needed_page(length) != g.first_needed_page(length - 1) for g in self.groups)
+        return any(g.first_needed_page(length) != g.first_needed_page(length - 1) and
+                   g.first_needed_page(length) > g.kept_pages() for g in self.groups)
 
     def truncate(self, slot: int, new_len: int) -> None:
         """Forgets the positions from ``new_len`` on (the reference's
@@ -258,7 +268,7 @@ class SequenceCache:
             raise CacheError("sequences with fixed-size state cannot be rewound")
         keep = (new_len + self.page_size - 1) // self.page_size
         for g in self.groups:
-            if any(p < 0 for p in g.pages[slot][g.first_needed_page(new_len):keep]):
+            if any(p < 0 for p in g.pages[slot][:min(g.kept_pages(), keep)] + g.pages[slot][g.first_needed_page(new_len):keep]):
                 raise CacheError("a windowed group already gave back pages needed at that length")
         for g in self.groups:
             pages = g.pages[slot]

@@ -339,4 +339,47 @@ int exl3_maps_prep(const void* x, int x_dtype, int64_t ld, int q_off, int k_off,
 int exl3_diff_combine(const void* a, int a_dtype, int a_row, const void* gate, int gate_dtype, int64_t gate_ld,
                       float lambda, float eps, float mult, void* out, int out_dtype, int out_row, int T, int heads,
                       int dv, cudaStream_t stream);
+
+// exl3_attn_tokens_wide with three more options: with a window, keys at positions below keep_first stay visible; softcap > 0
+// replaces a score s (after the scale) by softcap * tanh(s / softcap); sink_vals [heads] (float32, with sink) are the
+// sink's scores per query head instead of 0.  max_splits must count the chunks of the kept keys too.
+int exl3_attn_tokens_opt(const void* q, int64_t q_row_stride, void* out, int out_f32, int dtype, const void* k_pool,
+                         const void* v_pool, const int* block_table, int bt_stride, const int* tok_pos,
+                         const int* tok_seq, int T, int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page,
+                         int window, int chunk, int sink, float scale, int split_keys, int max_splits, float* scratch,
+                         size_t scratch_bytes, int keep_first, float softcap, const float* sink_vals, cudaStream_t stream);
+
+// rows of gu are [gate (I) | up (I)], ld elements apart: out = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit)
+// and u = clamp(up, -limit, limit).
+int exl3_clamped_glu(const void* gu, int in_dtype, int64_t ld, void* out, int out_dtype, int T, int I, float limit,
+                     float alpha, cudaStream_t stream);
+
+// Hyper-connections (see hyper.cu): the write of a sublayer's output y into all S streams of x (mix [S, S] indexed
+// [from, to], w_out [S]) and/or the read r = rmsnorm(sum_s w_in[s] x_s) * norm_w that follows it.  xin is [T, s_in, W]
+// with s_in 1 (one row stands for S equal streams) or S; xout [T, S, W] may be xin.  rows (reads only): the tokens read.
+int exl3_hyper_max_streams();
+int exl3_hyper_step(const float* xin, int s_in, float* xout, int S, const void* y, int y_dtype, const float* mix,
+                    const float* w_out, const float* w_in, const void* norm_w, int norm_w_dtype, float eps, void* r,
+                    int r_dtype, const int* rows, int n_rows, int T, int W, cudaStream_t stream);
+
+// Recurrences with a matrix state per head (see matrix_memory.cu).  q, k, v: rows of a step's packed tokens with their own
+// pitches; states float32 per slot; out float32 [T, heads * dv].
+int exl3_mlstm_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, int qkv_dtype,
+                    const void* zi, const void* zf, int gate_dtype, int64_t ld_gate, float cap, float q_scale,
+                    float* s_state, float* n_state, float* m_state, const int* slot_ids, const int* row_start,
+                    float* out, int rows, int T, int heads, int dk, int dv, cudaStream_t stream);
+int exl3_delta_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, int qkv_dtype,
+                    const void* zb, int zb_dtype, int64_t ld_zb, const void* za, int za_dtype, int64_t ld_za,
+                    const float* a_log, const float* dt_bias, float* s_state, const int* slot_ids, const int* row_start,
+                    float* out, int rows, int T, int heads, int qk_heads, int dk, int dv, cudaStream_t stream);
+// Short causal convolution per channel, SiLU, unit q and k heads (see matrix_memory.cu).  out float32 [T, 2 qk_heads dk +
+// v_heads dv]; state float32 [slots, channels, n_taps - 1].
+int exl3_conv_prep_max_taps();
+int exl3_conv_prep(const void* x, int x_dtype, int64_t ldx, int q_off, int k_off, int v_off, const float* q_taps,
+                   const float* k_taps, const float* v_taps, int qk_heads, int dk, int v_heads, int dv, int n_taps,
+                   float eps, float q_scale, float* state, const int* slot_ids, const int* row_start, float* out,
+                   int rows, int T, int max_new, cudaStream_t stream);
+// out = sa * a + sb * b element by element, float32 out.
+int exl3_scaled_sum2(const void* a, const void* b, int ab_dtype, float sa, float sb, float* out, int64_t n,
+                     cudaStream_t stream);
 }

@@ -30,6 +30,12 @@
 //              counted from the start of the sequence), on top of the causal bound and the window;
 //   sink:      one is added to the softmax's denominator, as if there were one more key with score 0 and a value
 //              of zero: p_j = exp(s_j) / (1 + sum_j exp(s_j)).
+// The entry point with every option (exl3_attn_tokens_opt) takes three more:
+//   keep_first > 0: with a window, the keys at positions below keep_first stay visible to every later query (at their
+//              true positions): j is seen when j <= pos and (pos - j < window or j < keep_first);
+//   softcap > 0: s <- softcap * tanh(s / softcap) after the scale;
+//   sink_vals: with sink, the sink's score per query head (not scaled, not capped) instead of 0:
+//              p_j = exp(s_j) / (exp(sink_h) + sum_j exp(s_j)).
 #include "api.h"
 #include "common.cuh"
 
@@ -61,11 +67,16 @@ template <> struct SoftmaxExp<__nv_bfloat16> {
 // The last step of a row with a sink: the sink enters as one more key of score 0 (in either base) whose value is
 // zero.  Returns the factor for the accumulator; the denominator comes back in l.
 template <typename T>
-__device__ inline float sink_finish(float m, float& l) {
-  const float mn = fmaxf(m, 0.0f);
+__device__ inline float sink_finish(float m, float& l, float sv = 0.0f) {
+  const float mn = fmaxf(m, sv);
   const float cs = SoftmaxExp<T>::exp(m - mn);
-  l = l * cs + SoftmaxExp<T>::exp(-mn);
+  l = l * cs + SoftmaxExp<T>::exp(sv - mn);
   return cs;
+}
+// The sink's score of a head in the softmax's units (0 without a table of them).
+template <typename T>
+__device__ inline float sink_score(const float* sink_vals, int head) {
+  return sink_vals ? __ldg(sink_vals + head) * SoftmaxExp<T>::prescale : 0.0f;
 }
 
 // An output element in the cache's type or, for callers that go on in float32 (maps that are subtracted from one
@@ -96,7 +107,8 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
                    const int* __restrict__ block_table, int bt_stride, const int* __restrict__ tok_pos,
                    const int* __restrict__ tok_seq, int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page,
                    int window, int chunk, int sink, float scale, int split_keys, int max_splits,
-                   float* __restrict__ scratch, int* __restrict__ counters, int lpk, int out_f32) {
+                   float* __restrict__ scratch, int* __restrict__ counters, int lpk, int out_f32, int keep_first,
+                   float softcap, const float* __restrict__ sink_vals) {
   constexpr int VEC = Elem<T>::vec;
   constexpr int NA = R * VEC;
   constexpr int U = R == 1 ? 4 : (R == 2 ? 2 : 1);  // key groups whose loads are issued together
@@ -114,12 +126,24 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
   int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
   if (chunk > 0) lo = max(lo, pos / chunk * chunk);
   const int hi = pos + 1;
-  // this block's chunk of keys
-  int c_lo = lo, c_hi = hi;
+  // kept first keys that the window no longer reaches: [0, kf); the visible keys are [0, kf) and [lo, hi)
+  const int kf = (window > 0 && keep_first > 0) ? min(keep_first, lo) : 0;
+  const float cap_mul = softcap > 0.0f ? softcap * SoftmaxExp<T>::prescale : 0.0f;
+  const float cap_in = softcap > 0.0f ? scale / softcap : 0.0f;
+  // this block's chunk of keys: the chunks of the kept keys that lie wholly before the window's first chunk come
+  // first, then the window's chunks; every chunk is aligned to absolute positions
+  int c_lo = kf > 0 ? 0 : lo, c_hi = hi;
   if (split_keys > 0) {
-    const int c = lo / split_keys + sp;
-    c_lo = max(lo, c * split_keys);
-    c_hi = min(hi, (c + 1) * split_keys);
+    const int c0 = lo / split_keys;
+    const int ckf = min((kf + split_keys - 1) / split_keys, c0);
+    if (sp < ckf) {
+      c_lo = sp * split_keys;
+      c_hi = min(kf, (sp + 1) * split_keys);
+    } else {
+      const int c = c0 + sp - ckf;
+      c_lo = (kf > c * split_keys) ? c * split_keys : max(lo, c * split_keys);
+      c_hi = min(hi, (c + 1) * split_keys);
+    }
   }
   const int* bt = block_table + (int64_t)tok_seq[t] * bt_stride;
   const int rec = hdv + 2;
@@ -153,6 +177,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
     if (c_lo < c_hi) {
       const int first_page = c_lo / page, last_page = (c_hi - 1) / page;
       for (int pi = first_page + warp; pi <= last_page; pi += ATT_WARPS) {
+        if (pi * page >= kf && (pi + 1) * page <= lo) continue;      // wholly between the kept keys and the window
         const int pg = bt[pi];
         const int64_t page_base = ((int64_t)pg * nkv + g) * page * kv_row;
         const int64_t page_base_v = ((int64_t)pg * nkv + g) * page * v_row;
@@ -164,7 +189,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
           for (int u = 0; u < U; ++u) {
             const int jj = jj0 + u * kpw;
             const int j = pi * page + jj;
-            valid[u] = (jj < page) && (j >= c_lo) && (j < c_hi) && (pg >= 0);
+            valid[u] = (jj < page) && (j >= c_lo) && (j < c_hi) && (j >= lo || j < kf) && (pg >= 0);
 #pragma unroll
             for (int r = 0; r < R; ++r) {
               const int d = (r * lpk + li) * VEC;
@@ -194,7 +219,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
               for (int i = 0; i < NA; ++i) s = fmaf(qv[hh][i], kv[i], s);
               for (int o = lpk >> 1; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
               if (valid[u]) {
-                s *= scale_eff;
+                s = cap_mul > 0.0f ? cap_mul * tanhf(s * cap_in) : s * scale_eff;
                 const float mn = fmaxf(m[hh], s);
                 const float corr = SoftmaxExp<T>::exp(m[hh] - mn);    // exp(-inf) = 0 on the first key
                 const float p = SoftmaxExp<T>::exp(s - mn);
@@ -263,7 +288,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
       }
       const int head = g * G + h0 + hh;
       if (max_splits <= 1) {
-        if (sink) aa *= sink_finish<T>(mm, ll);
+        if (sink) aa *= sink_finish<T>(mm, ll, sink_score<T>(sink_vals, head));
         att_store<T>(out, out_f32, ((int64_t)t * nh + head) * hdv + d, aa / ll);
       } else {
         float* sc = scratch + (((int64_t)t * nh + head) * max_splits + sp) * rec;
@@ -300,7 +325,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
     __syncthreads();
     float ll = 0.0f;
     for (int s2 = 0; s2 < max_splits; ++s2) ll += sl[s2] * sw[s2];
-    const float fin = sink ? sink_finish<T>(mx, ll) : 1.0f;
+    const float fin = sink ? sink_finish<T>(mx, ll, sink_score<T>(sink_vals, head)) : 1.0f;
     for (int d = threadIdx.x; d < hdv; d += blockDim.x) {
       float aa = 0.0f;
 #pragma unroll 4
@@ -316,7 +341,7 @@ attn_tokens_kernel(const T* __restrict__ q, int64_t q_row_stride, T* __restrict_
 // both sums in chunk order.  The records are read with independent loads.
 template <typename T>
 __global__ void attn_combine_kernel(const float* __restrict__ scratch, T* __restrict__ out, int nh, int hd,
-                                    int max_splits, int sink, int out_f32) {
+                                    int max_splits, int sink, int out_f32, const float* __restrict__ sink_vals) {
   extern __shared__ float sw[];                      // [max_splits] weights, then [max_splits] sums
   pdl_wait();
   pdl_trigger();
@@ -336,7 +361,7 @@ __global__ void attn_combine_kernel(const float* __restrict__ scratch, T* __rest
   __syncthreads();
   float ll = 0.0f;
   for (int s = 0; s < max_splits; ++s) ll += sl[s] * sw[s];
-  const float fin = sink ? sink_finish<T>(mx, ll) : 1.0f;
+  const float fin = sink ? sink_finish<T>(mx, ll, sink_score<T>(sink_vals, head)) : 1.0f;
   for (int d = threadIdx.x; d < hd; d += blockDim.x) {
     float aa = 0.0f;
 #pragma unroll 4
@@ -350,7 +375,7 @@ static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const v
                          const void* v_pool, const int* block_table, int bt_stride, const int* tok_pos,
                          const int* tok_seq, int T_, int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page,
                          int window, int chunk, int sink, float scale, int split_keys, int max_splits, float* scratch, int lpk,
-                         int out_f32, cudaStream_t stream) {
+                         int out_f32, int keep_first, float softcap, const float* sink_vals, cudaStream_t stream) {
   const size_t smem = ((size_t)ATT_WARPS * GT * (hdv + 2) + 2 * (size_t)max_splits) * sizeof(float);
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(attn_tokens_kernel<T, GT, R>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -369,12 +394,13 @@ static int launch_tokens(const void* q, int64_t q_row_stride, void* out, const v
   launch_pdl(attn_tokens_kernel<T, GT, R>, grid, dim3(ATT_WARPS * 32), smem, stream,
              static_cast<const T*>(q), q_row_stride, static_cast<T*>(out), static_cast<const T*>(k_pool),
              static_cast<const T*>(v_pool), block_table, bt_stride, tok_pos, tok_seq, nh, nkv, hd, hdv, kv_row, v_row, page,
-             window, chunk, sink, scale, split_keys, max_splits, scratch, counters, lpk, out_f32);
+             window, chunk, sink, scale, split_keys, max_splits, scratch, counters, lpk, out_f32, keep_first, softcap,
+             sink_vals);
   int rc = launch_status("attn_tokens");
   if (rc) return rc;
   if (max_splits > 1 && !fused_merge) {
     launch_pdl(attn_combine_kernel<T>, dim3(T_, nh), dim3(64), (size_t)2 * max_splits * sizeof(float), stream,
-               (const float*)scratch, static_cast<T*>(out), nh, hdv, max_splits, sink, out_f32);
+               (const float*)scratch, static_cast<T*>(out), nh, hdv, max_splits, sink, out_f32, sink_vals);
     rc = launch_status("attn_combine");
   }
   return rc;
@@ -384,7 +410,8 @@ template <typename T>
 static int dispatch(const void* q, int64_t q_row_stride, void* out, const void* k_pool, const void* v_pool,
                     const int* block_table, int bt_stride, const int* tok_pos, const int* tok_seq, int T_,
                     int nh, int nkv, int hd, int hdv, int kv_row, int v_row, int page, int window, int chunk, int sink,
-                    float scale, int split_keys, int max_splits, float* scratch, int out_f32, cudaStream_t stream) {
+                    float scale, int split_keys, int max_splits, float* scratch, int out_f32, int keep_first, float softcap,
+                    const float* sink_vals, cudaStream_t stream) {
   constexpr int VEC = Elem<T>::vec;
   const int vecs = ceil_div(max(hd, hdv), VEC);       // 16-byte pieces of the wider of a key row and a value row
   int lpk = 1;
@@ -394,7 +421,7 @@ static int dispatch(const void* q, int64_t q_row_stride, void* out, const void* 
 #define EXL3_ATT(GT, RR)                                                                                 \
   return launch_tokens<T, GT, RR>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos, \
                                   tok_seq, T_, nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale, \
-                                  split_keys, max_splits, scratch, lpk, out_f32, stream)
+                                  split_keys, max_splits, scratch, lpk, out_f32, keep_first, softcap, sink_vals, stream)
   if (R == 1) {
     if (G == 1) EXL3_ATT(1, 1);
     if (G == 2) EXL3_ATT(2, 1);
@@ -429,13 +456,18 @@ extern "C" size_t exl3_attn_tokens_scratch_bytes(int T, int nh, int hd, int max_
   return (size_t)ATT_COUNTER_SLOTS * sizeof(int) + (size_t)T * nh * max_splits * (hd + 2) * sizeof(float);
 }
 
-extern "C" int exl3_attn_tokens_wide(const void* q, int64_t q_row_stride, void* out, int out_f32, int dtype,
-                                     const void* k_pool, const void* v_pool, const int* block_table,
-                                     int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
-                                     int hd, int hdv, int kv_row, int v_row, int page, int window, int chunk, int sink,
-                                     float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
-                                     cudaStream_t stream) {
+extern "C" int exl3_attn_tokens_opt(const void* q, int64_t q_row_stride, void* out, int out_f32, int dtype,
+                                    const void* k_pool, const void* v_pool, const int* block_table,
+                                    int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
+                                    int hd, int hdv, int kv_row, int v_row, int page, int window, int chunk, int sink,
+                                    float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
+                                    int keep_first, float softcap, const float* sink_vals, cudaStream_t stream) {
   if (T == 0) return 0;
+  if (keep_first < 0 || softcap < 0.0f || (sink_vals != nullptr && !sink)) {
+    set_error("attn_tokens: keep_first %d and softcap %g must not be negative, and sink scores need the sink", keep_first,
+              (double)softcap);
+    return ERR_BAD_ARGUMENT;
+  }
   if (T < 0 || nh < 1 || nkv < 1 || nh % nkv != 0 || hd < 8 || hd % 8 != 0 || hdv < 8 || hdv % 8 != 0 ||
       kv_row < hd || kv_row % 8 != 0 || v_row < hdv || v_row % 8 != 0 || page < 1 || window < 0 || chunk < 0 ||
       max_splits < 1 || split_keys < 0 || (max_splits > 1 && split_keys == 0)) {
@@ -462,13 +494,24 @@ extern "C" int exl3_attn_tokens_wide(const void* q, int64_t q_row_stride, void* 
   if (dtype == DT_F32)
     return dispatch<float>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq, T,
                            nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale, split_keys, max_splits,
-                           scratch, out_f32, stream);
+                           scratch, out_f32, keep_first, softcap, sink_vals, stream);
   if (dtype == DT_BF16)
     return dispatch<__nv_bfloat16>(q, q_row_stride, out, k_pool, v_pool, block_table, bt_stride, tok_pos,
                                    tok_seq, T, nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale,
-                                   split_keys, max_splits, scratch, out_f32, stream);
+                                   split_keys, max_splits, scratch, out_f32, keep_first, softcap, sink_vals, stream);
   set_error("attn_tokens: unsupported element type %d", dtype);
   return ERR_UNSUPPORTED;
+}
+
+extern "C" int exl3_attn_tokens_wide(const void* q, int64_t q_row_stride, void* out, int out_f32, int dtype,
+                                     const void* k_pool, const void* v_pool, const int* block_table,
+                                     int bt_stride, const int* tok_pos, const int* tok_seq, int T, int nh, int nkv,
+                                     int hd, int hdv, int kv_row, int v_row, int page, int window, int chunk, int sink,
+                                     float scale, int split_keys, int max_splits, float* scratch, size_t scratch_bytes,
+                                     cudaStream_t stream) {
+  return exl3_attn_tokens_opt(q, q_row_stride, out, out_f32, dtype, k_pool, v_pool, block_table, bt_stride, tok_pos, tok_seq,
+                              T, nh, nkv, hd, hdv, kv_row, v_row, page, window, chunk, sink, scale, split_keys, max_splits,
+                              scratch, scratch_bytes, 0, 0.0f, nullptr, stream);
 }
 
 extern "C" int exl3_attn_tokens_ex(const void* q, int64_t q_row_stride, void* out, int dtype,

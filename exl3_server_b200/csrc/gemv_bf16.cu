@@ -40,10 +40,10 @@ extern "C" int exl3_gemv_bf16_act(const void* x, const void* w, const void* bias
   return gemv_act(x, w, bias, y, out_dtype, M, N, K, act_p, act_n, 0, stream);
 }
 
-// The same with GELU on the results: kind 0 exact (erf), 1 by the tanh formula.
+// The same with GELU on the results: kind 0 exact (erf), 1 by the tanh formula; kind 2: the square of relu.
 extern "C" int exl3_gemv_bf16_gelu(const void* x, const void* w, const void* bias, void* y, int out_dtype, int M,
                                    int N, int K, int kind, cudaStream_t stream) {
-  if (kind < 0 || kind > 1) { set_error("gemv_bf16_gelu: kind is 0 (erf) or 1 (tanh)"); return ERR_BAD_ARGUMENT; }
+  if (kind < 0 || kind > 2) { set_error("gemv_bf16_gelu: kind is 0 (erf), 1 (tanh) or 2 (relu squared)"); return ERR_BAD_ARGUMENT; }
   return gemv_act(x, w, bias, y, out_dtype, M, N, K, 0.0f, 0.0f, 1 + kind, stream);
 }
 

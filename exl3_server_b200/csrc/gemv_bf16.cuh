@@ -81,6 +81,7 @@ struct GemvNorm {
 __device__ inline float gemv_activation(float s, float act_p, float act_n, int kind) {
   if (kind == 1) return 0.5f * s * (1.0f + erff(s * 0.70710678118654752f));
   if (kind == 2) return 0.5f * s * (1.0f + tanhf(0.79788456080286536f * (s + 0.044715f * s * s * s)));
+  if (kind == 3) { const float r = fmaxf(s, 0.0f); return r * r; }
   return s > 0.0f ? fmaf(act_p * s, s, 0.5f * s) : fmaf(act_n, expm1f(s) - s, 0.5f * s);
 }
 

@@ -50,6 +50,10 @@ __device__ inline void warp_argmax(float& v, int& i) {
 __device__ inline void route_choice(int t, int lane, float* zt, float* ct, float* gst, float* gkt,
                                     const float* __restrict__ corr, int E, int S, int groups, int keep, int top,
                                     float scale, int score_kind, int* idx, float* wt, float* gate_out) {
+  // score_kind: bit 0 set: sigmoid scores (else softmax); bit 1 set: a group's score is the sum of its two largest
+  // choice scores (else its largest)
+  const bool group_pair = (score_kind & 2) != 0;
+  score_kind &= 1;
   if (S && lane == 0) gate_out[t] = 1.0f / (1.0f + expf(-zt[E]));
   if (score_kind == 0) {
     float mx = -INFINITY;
@@ -78,9 +82,12 @@ __device__ inline void route_choice(int t, int lane, float* zt, float* ct, float
   if (groups > 1 && keep < groups) {
     const int per = E / groups;
     for (int g = lane; g < groups; g += 32) {
-      float m = -INFINITY;
-      for (int e = g * per; e < (g + 1) * per; ++e) m = fmaxf(m, ct[e]);
-      gst[g] = m;
+      float m = -INFINITY, m2 = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float v = ct[e];
+        if (v > m) { m2 = m; m = v; } else if (v > m2) m2 = v;
+      }
+      gst[g] = (group_pair && per > 1) ? m + m2 : m;
       gkt[g] = 0.0f;
     }
     __syncwarp();
@@ -498,7 +505,7 @@ extern "C" int exl3_moe_route(const void* x, int x_dtype, int64_t ldx, const flo
                               float* wt, float* gate_out, cudaStream_t stream) {
   if (T == 0) return 0;
   if (T < 0 || W < 1 || E < 1 || extra < 0 || extra > 1 || groups < 1 || E % groups != 0 || keep < 1 || keep > groups ||
-      top < 1 || top > keep * (E / groups) || (extra && gate_out == nullptr) || score_kind < 0 || score_kind > 1) {
+      top < 1 || top > keep * (E / groups) || (extra && gate_out == nullptr) || score_kind < 0 || score_kind > 3) {
     set_error("moe_route: bad sizes T=%d width=%d outputs=%d groups=%d keep=%d top=%d", T, W, E, groups, keep, top);
     return ERR_BAD_ARGUMENT;
   }
@@ -647,4 +654,88 @@ extern "C" int exl3_moe_combine(const float* y, const int* idx, const float* wt,
   else { if (vec) EXL3_COMBINE(__nv_bfloat16, 4); else EXL3_COMBINE(__nv_bfloat16, 1); }
 #undef EXL3_COMBINE
   return launch_status("moe_combine");
+}
+
+// The activation of experts with a bounded gate: rows of gu hold [gate (I) | up (I)];
+//   g = min(gate, limit), u = clamp(up, -limit, limit), out = g * sigmoid(alpha * g) * (u + 1)
+// float32 inside.  Four features a thread where the sizes allow 8- or 16-byte accesses.
+namespace exl3 {
+
+template <typename T> __device__ inline void cg_load4(const T* p, float (&v)[4]);
+template <> __device__ inline void cg_load4<float>(const float* p, float (&v)[4]) { load_vec_cg(p, v); }
+template <> __device__ inline void cg_load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+  const uint2 r = __ldcg(reinterpret_cast<const uint2*>(p));
+  v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+  v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+}
+template <typename T> __device__ inline void cg_store4(T* p, const float (&v)[4]);
+template <> __device__ inline void cg_store4<float>(float* p, const float (&v)[4]) { store_vec(p, v); }
+template <> __device__ inline void cg_store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+  __nv_bfloat162 lo = __floats2bfloat162_rn(v[0], v[1]), hi = __floats2bfloat162_rn(v[2], v[3]);
+  uint2 r;
+  r.x = *reinterpret_cast<uint32_t*>(&lo);
+  r.y = *reinterpret_cast<uint32_t*>(&hi);
+  *reinterpret_cast<uint2*>(p) = r;
+}
+
+__device__ inline float clamped_glu_one(float g, float u, float limit, float alpha) {
+  g = fminf(g, limit);
+  u = fminf(fmaxf(u, -limit), limit);
+  return g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+}
+
+template <typename TI, typename TO, int V>
+__global__ void __launch_bounds__(256)
+clamped_glu_kernel(const TI* __restrict__ gu, int64_t ld, TO* __restrict__ out, int T, int I, float limit, float alpha) {
+  pdl_wait();
+  pdl_trigger();
+  const int per_row = I / V;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (int64_t)T * per_row) return;
+  const int64_t t = idx / per_row;
+  const int c = (int)(idx - t * per_row) * V;
+  if (V == 4) {
+    float g[4], u[4], y[4];
+    cg_load4<TI>(gu + t * ld + c, g);
+    cg_load4<TI>(gu + t * ld + I + c, u);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) y[e] = clamped_glu_one(g[e], u[e], limit, alpha);
+    cg_store4<TO>(out + t * I + c, y);
+  } else {
+    const float g = Elem<TI>::load(gu + t * ld + c), u = Elem<TI>::load(gu + t * ld + I + c);
+    Elem<TO>::store(out + t * I + c, clamped_glu_one(g, u, limit, alpha));
+  }
+}
+
+template <typename TI, typename TO>
+static int clamped_glu_launch(const void* gu, int64_t ld, void* out, int T, int I, float limit, float alpha, bool vec,
+                              cudaStream_t stream) {
+  const int64_t total = (int64_t)T * (I / (vec ? 4 : 1));
+  const int64_t blocks = (total + 255) / 256;
+  if (blocks > 0x7fffffffLL) { set_error("clamped_glu: too many elements"); return ERR_UNSUPPORTED; }
+  if (vec)
+    launch_pdl(clamped_glu_kernel<TI, TO, 4>, dim3((unsigned)blocks), dim3(256), 0, stream, static_cast<const TI*>(gu), ld,
+               static_cast<TO*>(out), T, I, limit, alpha);
+  else
+    launch_pdl(clamped_glu_kernel<TI, TO, 1>, dim3((unsigned)blocks), dim3(256), 0, stream, static_cast<const TI*>(gu), ld,
+               static_cast<TO*>(out), T, I, limit, alpha);
+  return launch_status("clamped_glu");
+}
+
+}  // namespace exl3
+
+extern "C" int exl3_clamped_glu(const void* gu, int in_dtype, int64_t ld, void* out, int out_dtype, int T, int I,
+                                float limit, float alpha, cudaStream_t stream) {
+  if (T == 0) return 0;
+  if (T < 0 || I < 1 || ld < 2 * (int64_t)I || !(limit > 0.0f)) {
+    set_error("clamped_glu: bad sizes rows=%d inner=%d pitch=%lld limit=%g", T, I, (long long)ld, (double)limit);
+    return ERR_BAD_ARGUMENT;
+  }
+  const bool vec = I % 4 == 0 && ld % 4 == 0 && aligned16(gu) && aligned16(out);
+  if (in_dtype == DT_F32 && out_dtype == DT_F32) return clamped_glu_launch<float, float>(gu, ld, out, T, I, limit, alpha, vec, stream);
+  if (in_dtype == DT_F32 && out_dtype == DT_BF16) return clamped_glu_launch<float, __nv_bfloat16>(gu, ld, out, T, I, limit, alpha, vec, stream);
+  if (in_dtype == DT_BF16 && out_dtype == DT_BF16) return clamped_glu_launch<__nv_bfloat16, __nv_bfloat16>(gu, ld, out, T, I, limit, alpha, vec, stream);
+  if (in_dtype == DT_BF16 && out_dtype == DT_F32) return clamped_glu_launch<__nv_bfloat16, float>(gu, ld, out, T, I, limit, alpha, vec, stream);
+  set_error("clamped_glu: unsupported element types %d -> %d", in_dtype, out_dtype);
+  return ERR_UNSUPPORTED;
 }

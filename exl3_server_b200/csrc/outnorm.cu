@@ -349,10 +349,12 @@ normed_sum2_kernel(const void* a, const void* b, int ab_dtype, const void* __res
   }
 }
 
-// Element-wise activations, float32 inside: GELU exact (erf, kind 0) or by the tanh formula (1), and tanh (2).
+// Element-wise activations, float32 inside: GELU exact (erf, kind 0) or by the tanh formula (1), tanh (2), and the
+// square of relu (3).
 __device__ inline float act_apply(float v, int kind) {
   if (kind == 0) return 0.5f * v * (1.0f + erff(v * 0.70710678118654752f));
   if (kind == 1) return 0.5f * v * (1.0f + tanhf(0.79788456080286536f * (v + 0.044715f * v * v * v)));
+  if (kind == 3) { const float r = fmaxf(v, 0.0f); return r * r; }
   return tanhf(v);
 }
 
@@ -430,9 +432,43 @@ extern "C" int exl3_normed_sum2(const void* a, const void* b, int ab_dtype, cons
   return launch_status("normed_sum2");
 }
 
+// out[t] = sa * a[t] + sb * b[t], float32 (two sublayer outputs side by side with a constant each).
+__global__ void __launch_bounds__(256)
+scaled_sum2_kernel(const void* a, const void* b, int ab_dtype, float sa, float sb, float* out, int64_t n) {
+  pdl_wait();
+  pdl_trigger();
+  const int64_t i = ((int64_t)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+  if (i >= n) return;
+  if (i + 4 <= n && ab_dtype == DT_F32) {
+    float x[4], y[4], o[4];
+    load_vec_cg(static_cast<const float*>(a) + i, x);
+    load_vec_cg(static_cast<const float*>(b) + i, y);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) o[e] = fmaf(sb, y[e], sa * x[e]);
+    store_vec(out + i, o);
+    return;
+  }
+  for (int64_t e = i; e < n && e < i + 4; ++e)
+    out[e] = fmaf(sb, on_load_act(b, ab_dtype, e), sa * on_load_act(a, ab_dtype, e));
+}
+
+extern "C" int exl3_scaled_sum2(const void* a, const void* b, int ab_dtype, float sa, float sb, float* out, int64_t n,
+                                cudaStream_t stream) {
+  if (n == 0) return 0;
+  if (n < 0 || a == nullptr || b == nullptr || out == nullptr || (ab_dtype != DT_F32 && ab_dtype != DT_BF16) ||
+      !aligned16(a) || !aligned16(b) || !aligned16(out)) {
+    set_error("scaled_sum2: bad arguments n=%lld", (long long)n);
+    return ERR_BAD_ARGUMENT;
+  }
+  const int64_t blocks = (n / 4 + 1 + 255) / 256;
+  if (blocks > 0x7fffffffLL) { set_error("scaled_sum2: too many elements"); return ERR_UNSUPPORTED; }
+  launch_pdl(scaled_sum2_kernel, dim3((unsigned)blocks), dim3(256), 0, stream, a, b, ab_dtype, sa, sb, out, n);
+  return launch_status("scaled_sum2");
+}
+
 extern "C" int exl3_activation(const void* z, int z_dtype, void* out, int out_dtype, int64_t n, int kind, cudaStream_t stream) {
   if (n == 0) return 0;
-  if (n < 0 || kind < 0 || kind > 2) { set_error("activation: bad arguments"); return ERR_BAD_ARGUMENT; }
+  if (n < 0 || kind < 0 || kind > 3) { set_error("activation: bad arguments"); return ERR_BAD_ARGUMENT; }
   if (n % 8 == 0 && aligned16(z) && aligned16(out)) {
     const int64_t n8 = n / 8;
     int64_t blocks = (n8 + 255) / 256;

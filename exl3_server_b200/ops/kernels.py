@@ -521,23 +521,28 @@ def attn_tokens_ex(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_pool
                    v_pool: torch.Tensor, block_table: torch.Tensor, tok_pos: torch.Tensor, tok_seq: torch.Tensor,
                    T: int, heads: int, kv_heads: int, head_dim: int, value_dim: int, page: int, window: int,
                    chunk: int, sink: bool, scale: float, split_keys: int, max_splits: int,
-                   scratch: Optional[torch.Tensor]) -> torch.Tensor:
+                   scratch: Optional[torch.Tensor], keep_first: int = 0, softcap: float = 0.0,
+                   sink_vals: Optional[torch.Tensor] = None) -> torch.Tensor:
     """``attn_tokens`` in its general form: rows of the key pool hold ``head_dim`` features and rows of the value
     pool ``value_dim`` (each pool's last dimension is its row pitch; multiples of 8; values may be wider than keys);
     ``chunk`` > 0 also hides every key before ``floor(pos / chunk) * chunk``; ``sink`` adds one to the softmax's
-    denominator.  ``out`` is ``[T, heads, value_dim]`` in the cache's type or float32 (for callers that go on in
-    float32) and the scratch is sized with ``value_dim``."""
+    denominator (``sink_vals`` float32 ``[heads]``: ``exp`` of a score per head instead of one).  With a window,
+    keys at positions below ``keep_first`` stay visible (``max_splits`` then counts their chunks too); ``softcap``
+    > 0 caps the scaled scores, ``c tanh(s / c)``.  ``out`` is ``[T, heads, value_dim]`` in the cache's type or
+    float32 (for callers that go on in float32) and the scratch is sized with ``value_dim``."""
+    if sink_vals is not None and (sink_vals.dtype != torch.float32 or sink_vals.numel() != heads or not sink):
+        raise KernelLibraryError("attn_tokens_ex: sink scores must be float32 [heads], with the sink on")
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype not in (q.dtype, torch.float32):
         raise KernelLibraryError("attn_tokens_ex: q, cache and out differ in element type")
     nbytes = 0 if scratch is None else scratch.numel() * scratch.element_size()
-    _check(library().exl3_attn_tokens_wide(
+    _check(library().exl3_attn_tokens_opt(
         _ptr(q), _c_int64(q_row_stride), _ptr(out), _c_int(1 if out.dtype == torch.float32 else 0),
         _c_int(dtype_code(q.dtype)), _ptr(k_pool), _ptr(v_pool),
         _ptr(block_table), _c_int(block_table.stride(0)), _ptr(tok_pos), _ptr(tok_seq), _c_int(T),
         _c_int(heads), _c_int(kv_heads), _c_int(head_dim), _c_int(value_dim), _c_int(k_pool.shape[-1]),
         _c_int(v_pool.shape[-1]), _c_int(page), _c_int(window), _c_int(chunk), _c_int(1 if sink else 0),
-        _c_float(scale), _c_int(split_keys), _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), _stream()),
-        "attn_tokens_ex")
+        _c_float(scale), _c_int(split_keys), _c_int(max_splits), _ptr(scratch), _c_size_t(nbytes), _c_int(keep_first),
+        _c_float(softcap), _ptr(sink_vals), _stream()), "attn_tokens_ex")
     return out
 
 
@@ -693,12 +698,12 @@ def normed_sum2(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Te
     return out
 
 
-ACTIVATION_KINDS = {"gelu": 0, "gelu_tanh": 1, "tanh": 2}
+ACTIVATION_KINDS = {"gelu": 0, "gelu_tanh": 1, "tanh": 2, "relu2": 3}
 
 
 def activation(z: torch.Tensor, out_dtype: torch.dtype, kind: str) -> torch.Tensor:
     """An activation of every element, float32 inside: ``gelu`` (exact, by erf), ``gelu_tanh`` (the tanh formula)
-    or ``tanh``."""
+    ``tanh`` or ``relu2`` (the square of relu)."""
     _contig(z, "z")
     out = torch.empty(z.shape, dtype=out_dtype, device=z.device)
     _check(library().exl3_activation(_ptr(z), _c_int(dtype_code(z.dtype)), _ptr(out), _c_int(dtype_code(out.dtype)),
@@ -791,9 +796,9 @@ def norm_add_norm(h: torch.Tensor, y: torch.Tensor, weight: torch.Tensor, eps: f
 
 
 def gemv_bf16_gelu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor], out_dtype: torch.dtype,
-                   tanh: bool = False) -> torch.Tensor:
-    """``gelu(x @ w.T (+ bias))`` for at most 16 rows of x, the activation (exact, or by the tanh formula) in the
-    projection's own epilogue."""
+                   tanh: bool = False, relu2: bool = False) -> torch.Tensor:
+    """``gelu(x @ w.T (+ bias))`` for at most 16 rows of x, the activation (exact, or by the tanh formula; with
+    ``relu2`` the square of relu instead) in the projection's own epilogue."""
     M, K = x.shape
     N, K2 = w.shape
     if K != K2 or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
@@ -802,7 +807,7 @@ def gemv_bf16_gelu(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor
     _contig(w, "w")
     out = torch.empty((M, N), dtype=out_dtype, device=x.device)
     _check(library().exl3_gemv_bf16_gelu(_ptr(x), _ptr(w), _ptr(bias), _ptr(out), _c_int(dtype_code(out.dtype)),
-                                         _c_int(M), _c_int(N), _c_int(K), _c_int(1 if tanh else 0), _stream()),
+                                         _c_int(M), _c_int(N), _c_int(K), _c_int(2 if relu2 else (1 if tanh else 0)), _stream()),
            "gemv_bf16_gelu")
     return out
 
@@ -1118,6 +1123,7 @@ def softcap(x: torch.Tensor, cap: float) -> torch.Tensor:
 
 MOE_ACTIVATIONS = {"none": 0, "gelu": 1, "gelu_tanh": 2, "silu": 3}
 MOE_SCORES = {"softmax": 0, "sigmoid": 1}
+MOE_GROUP_SCORES = {"max": 0, "top2": 2}     # added to the score's code
 
 
 def moe_tile_rows(kind: str = "tile") -> int:
@@ -1141,10 +1147,11 @@ def moe_tc_status() -> int:
 
 
 def moe_route(x: torch.Tensor, wr: torch.Tensor, corr: torch.Tensor, outputs: int, extra: int, groups: int, keep: int,
-              top: int, scale: float, score: str = "softmax"):
+              top: int, scale: float, score: str = "softmax", group_score: str = "max"):
     """The router of a routed feed-forward (see moe.cu): ``wr`` float32 ``[outputs + extra, W]``, ``corr`` float32
     ``[outputs]`` added to the scores for the choice only.  Returns ``(idx int32 [T, top], weight float32 [T, top],
-    gate float32 [T] or None)``: the gate is the sigmoid of the extra row's product."""
+    gate float32 [T] or None)``: the gate is the sigmoid of the extra row's product.  ``group_score``: a group's
+    score is its largest choice score (``max``) or the sum of its two largest (``top2``)."""
     T, W = x.shape
     if x.stride(1) != 1:
         raise KernelLibraryError("moe_route: rows of x must be dense")
@@ -1158,7 +1165,8 @@ def moe_route(x: torch.Tensor, wr: torch.Tensor, corr: torch.Tensor, outputs: in
     _check(library().exl3_moe_route(
         _ptr(x), _c_int(dtype_code(x.dtype)), _c_int64(x.stride(0)), _ptr(wr), _ptr(corr), _c_int(T), _c_int(W),
         _c_int(outputs), _c_int(extra), _c_int(groups), _c_int(keep), _c_int(top), _c_float(scale),
-        _c_int(MOE_SCORES[score]), _ptr(idx), _ptr(wt), _ptr(gate), _stream()), "moe_route")
+        _c_int(MOE_SCORES[score] + MOE_GROUP_SCORES[group_score]), _ptr(idx), _ptr(wt), _ptr(gate), _stream()),
+        "moe_route")
     return idx, wt, gate
 
 
@@ -1301,4 +1309,155 @@ def diff_combine(a: torch.Tensor, a_row: int, gate: Optional[torch.Tensor], lam:
         _c_int(dtype_code(gate.dtype) if gate is not None else 0), _c_int64(gate.stride(0) if gate is not None else 0),
         _c_float(lam), _c_float(eps), _c_float(mult), _ptr(out), _c_int(dtype_code(out_dtype)), _c_int(out_row),
         _c_int(T), _c_int(heads), _c_int(dv), _stream()), "diff_combine")
+    return out
+
+
+def clamped_glu(gu: torch.Tensor, limit: float, alpha: float, out_dtype: torch.dtype) -> torch.Tensor:
+    """``g * sigmoid(alpha g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)`` for rows
+    ``[gate (I) | up (I)]`` of ``gu`` (float32 inside)."""
+    T, two = gu.shape
+    if gu.stride(1) != 1 or two % 2:
+        raise KernelLibraryError("clamped_glu: rows of gu must be dense and hold a gate half and an up half")
+    out = torch.empty((T, two // 2), dtype=out_dtype, device=gu.device)
+    _check(library().exl3_clamped_glu(_ptr(gu), _c_int(dtype_code(gu.dtype)), _c_int64(gu.stride(0)), _ptr(out),
+                                      _c_int(dtype_code(out_dtype)), _c_int(T), _c_int(two // 2), _c_float(limit),
+                                      _c_float(alpha), _stream()), "clamped_glu")
+    return out
+
+
+def hyper_max_streams() -> int:
+    return int(library().exl3_hyper_max_streams())
+
+
+def hyper_step(x: torch.Tensor, streams: int, y: Optional[torch.Tensor], mix: Optional[torch.Tensor],
+               w_out: Optional[torch.Tensor], w_in: Optional[torch.Tensor], norm_w: Optional[torch.Tensor], eps: float,
+               out_dtype: torch.dtype, rows: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None):
+    """One step of a residual of several streams (see hyper.cu).  ``x`` float32 ``[T, streams * W]``; or, with ``out``
+    float32 ``[T, streams * W]`` given, ``[T, W]`` standing for ``streams`` equal ones (``out`` then gets the streams).  With ``y [T, W]``: every stream
+    becomes ``sum_s mix[s, to] x_s + w_out[to] y`` in place.  With ``w_in``: returns ``rmsnorm(sum_s w_in[s] x_s) *
+    norm_w`` in ``out_dtype``, of all tokens or of ``rows`` (only without ``y``).  Returns ``(streams tensor, r or
+    None)``."""
+    T = x.shape[0]
+    if x.dtype != torch.float32:
+        raise KernelLibraryError("hyper_step: the streams must be float32")
+    _contig(x, "x")
+    # with ``out`` given, x is one row per token that stands for ``streams`` equal ones and ``out`` gets the streams
+    s_in = 1 if out is not None else streams
+    W = x.shape[1] // s_in
+    if x.shape[1] != s_in * W or (out is not None and (tuple(out.shape) != (T, streams * W) or out.dtype != torch.float32
+                                                       or not out.is_contiguous())):
+        raise KernelLibraryError(f"hyper_step: x {tuple(x.shape)} does not hold {streams} streams")
+    xout = out if out is not None else x
+    for t, n in ((mix, streams * streams), (w_out, streams), (w_in, streams)):
+        if t is not None and (t.dtype != torch.float32 or t.numel() != n or not t.is_contiguous()):
+            raise KernelLibraryError("hyper_step: mix, w_out and w_in must be contiguous float32 of [S, S], [S], [S]")
+    if y is not None:
+        _contig(y, "y")
+        if tuple(y.shape) != (T, W) or mix is None or w_out is None:
+            raise KernelLibraryError("hyper_step: y must be [T, W] and come with mix and w_out")
+    if norm_w is not None and norm_w.numel() != W:
+        raise KernelLibraryError("hyper_step: the norm's weight must be [W]")
+    n = T if rows is None else rows.numel()
+    r = torch.empty((n, W), dtype=out_dtype, device=x.device) if w_in is not None else None
+    _check(library().exl3_hyper_step(
+        _ptr(x), _c_int(s_in), _ptr(xout), _c_int(streams), _ptr(y), _c_int(dtype_code(y.dtype) if y is not None else 0),
+        _ptr(mix), _ptr(w_out), _ptr(w_in), _ptr(norm_w), _c_int(dtype_code(norm_w.dtype) if norm_w is not None else 0),
+        _c_float(eps), _ptr(r), _c_int(dtype_code(out_dtype)), _ptr(rows), _c_int(n), _c_int(T), _c_int(W), _stream()),
+        "hyper_step")
+    return xout, r
+
+
+def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zi: torch.Tensor, zf: torch.Tensor, cap: float,
+               q_scale: float, s_state: torch.Tensor, n_state: torch.Tensor, m_state: torch.Tensor,
+               slot_ids: torch.Tensor, row_start: torch.Tensor, rows: int, heads: int, dk: int, dv: int) -> torch.Tensor:
+    """The matrix memory with exponential gates over a step's packed tokens (see matrix_memory.cu).  ``q``, ``k``
+    ``[T, heads * dk]``, ``v [T, heads * dv]`` and the gates' pre-activations ``zi``, ``zf [T, heads]`` may be views
+    with their own row pitch; states float32 ``[slots, heads, dk, dv]``, ``[slots, heads, dk]``, ``[slots, heads]``
+    are read and written at ``slot_ids``.  Returns float32 ``[T, heads * dv]``."""
+    T = q.shape[0]
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (zi, "zi"), (zf, "zf")):
+        if t.stride(1) != 1:
+            raise KernelLibraryError(f"mlstm_scan: rows of {name} must be dense")
+    if q.dtype != k.dtype or q.dtype != v.dtype or zi.dtype != zf.dtype or zi.stride(0) != zf.stride(0):
+        raise KernelLibraryError("mlstm_scan: q, k, v (and zi, zf) must agree in element type and pitch")
+    for t, shape in ((s_state, (heads, dk, dv)), (n_state, (heads, dk)), (m_state, (heads,))):
+        if t.dtype != torch.float32 or tuple(t.shape[1:]) != shape or not t.is_contiguous():
+            raise KernelLibraryError(f"mlstm_scan: a state of shape {tuple(t.shape)} must be contiguous float32 [slots, {shape}]")
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
+    _check(library().exl3_mlstm_scan(
+        _ptr(q), _c_int64(q.stride(0)), _ptr(k), _c_int64(k.stride(0)), _ptr(v), _c_int64(v.stride(0)),
+        _c_int(dtype_code(q.dtype)), _ptr(zi), _ptr(zf), _c_int(dtype_code(zi.dtype)), _c_int64(zi.stride(0)),
+        _c_float(cap), _c_float(q_scale), _ptr(s_state), _ptr(n_state), _ptr(m_state), _ptr(slot_ids), _ptr(row_start),
+        _ptr(out), _c_int(rows), _c_int(T), _c_int(heads), _c_int(dk), _c_int(dv), _stream()), "mlstm_scan")
+    return out
+
+
+def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zb: torch.Tensor, za: torch.Tensor,
+               a_log: torch.Tensor, dt_bias: torch.Tensor, s_state: torch.Tensor, slot_ids: torch.Tensor,
+               row_start: torch.Tensor, rows: int, heads: int, qk_heads: int, dk: int, dv: int) -> torch.Tensor:
+    """The gated delta rule over a step's packed tokens (see matrix_memory.cu): ``q``, ``k [T, qk_heads * dk]``,
+    ``v [T, heads * dv]`` (one element type), ``zb [T, heads]`` (beta before its sigmoid), ``za [T, heads * dk]``
+    (the decay's pre-activation, before ``dt_bias``), ``a_log [heads]``, ``dt_bias [heads * dk]`` float32; state
+    float32 ``[slots, heads, dk, dv]``.  Returns float32 ``[T, heads * dv]``."""
+    T = q.shape[0]
+    for t, name in ((q, "q"), (k, "k"), (v, "v"), (zb, "zb"), (za, "za")):
+        if t.stride(1) != 1:
+            raise KernelLibraryError(f"delta_scan: rows of {name} must be dense")
+    if q.dtype != k.dtype or q.dtype != v.dtype:
+        raise KernelLibraryError("delta_scan: q, k and v must agree in element type")
+    if a_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 or a_log.numel() != heads or \
+            dt_bias.numel() != heads * dk:
+        raise KernelLibraryError("delta_scan: a_log and dt_bias must be float32 [heads] and [heads * dk]")
+    if s_state.dtype != torch.float32 or tuple(s_state.shape[1:]) != (heads, dk, dv) or not s_state.is_contiguous():
+        raise KernelLibraryError(f"delta_scan: state {tuple(s_state.shape)} must be float32 [slots, {heads}, {dk}, {dv}]")
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
+    _check(library().exl3_delta_scan(
+        _ptr(q), _c_int64(q.stride(0)), _ptr(k), _c_int64(k.stride(0)), _ptr(v), _c_int64(v.stride(0)),
+        _c_int(dtype_code(q.dtype)), _ptr(zb), _c_int(dtype_code(zb.dtype)), _c_int64(zb.stride(0)), _ptr(za),
+        _c_int(dtype_code(za.dtype)), _c_int64(za.stride(0)), _ptr(a_log), _ptr(dt_bias), _ptr(s_state), _ptr(slot_ids),
+        _ptr(row_start), _ptr(out), _c_int(rows), _c_int(T), _c_int(heads), _c_int(qk_heads), _c_int(dk), _c_int(dv),
+        _stream()), "delta_scan")
+    return out
+
+
+def conv_prep_max_taps() -> int:
+    return int(library().exl3_conv_prep_max_taps())
+
+
+def conv_prep(x: torch.Tensor, q_off: int, k_off: int, v_off: int, q_taps: torch.Tensor, k_taps: torch.Tensor,
+              v_taps: torch.Tensor, qk_heads: int, dk: int, v_heads: int, dv: int, eps: float, q_scale: float,
+              state: torch.Tensor, slot_ids: torch.Tensor, row_start: torch.Tensor, rows: int,
+              max_new: int) -> torch.Tensor:
+    """Short causal convolutions per channel over a step's packed tokens, SiLU, and unit query and key heads (see
+    matrix_memory.cu).  ``x [T, *]`` holds the q, k and v channels from the given columns on; taps float32
+    ``[channels, taps]`` (the last tap is the current token's); ``state`` float32 ``[slots, channels, taps - 1]`` holds
+    every channel's last inputs and is kept up.  Returns float32 ``[T, 2 qk_heads dk + v_heads dv]``: q | k | v."""
+    T = x.shape[0]
+    if x.stride(1) != 1:
+        raise KernelLibraryError("conv_prep: rows of x must be dense")
+    n_taps = q_taps.shape[1]
+    C = 2 * qk_heads * dk + v_heads * dv
+    for t, n in ((q_taps, qk_heads * dk), (k_taps, qk_heads * dk), (v_taps, v_heads * dv)):
+        if t.dtype != torch.float32 or tuple(t.shape) != (n, n_taps) or not t.is_contiguous():
+            raise KernelLibraryError("conv_prep: taps must be contiguous float32 [channels, taps]")
+    if state.dtype != torch.float32 or tuple(state.shape[1:]) != (C, n_taps - 1) or not state.is_contiguous():
+        raise KernelLibraryError(f"conv_prep: state {tuple(state.shape)} must be float32 [slots, {C}, {n_taps - 1}]")
+    out = torch.empty((T, C), dtype=torch.float32, device=x.device)
+    _check(library().exl3_conv_prep(
+        _ptr(x), _c_int(dtype_code(x.dtype)), _c_int64(x.stride(0)), _c_int(q_off), _c_int(k_off), _c_int(v_off),
+        _ptr(q_taps), _ptr(k_taps), _ptr(v_taps), _c_int(qk_heads), _c_int(dk), _c_int(v_heads), _c_int(dv),
+        _c_int(n_taps), _c_float(eps), _c_float(q_scale), _ptr(state), _ptr(slot_ids), _ptr(row_start), _ptr(out),
+        _c_int(rows), _c_int(T), _c_int(max_new), _stream()), "conv_prep")
+    return out
+
+
+def scaled_sum2(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float) -> torch.Tensor:
+    """``sa * a + sb * b`` element by element, float32."""
+    _contig(a, "a")
+    _contig(b, "b")
+    if a.dtype != b.dtype or a.shape != b.shape:
+        raise KernelLibraryError("scaled_sum2: a and b must agree in shape and type")
+    out = torch.empty(a.shape, dtype=torch.float32, device=a.device)
+    _check(library().exl3_scaled_sum2(_ptr(a), _ptr(b), _c_int(dtype_code(a.dtype)), _c_float(sa), _c_float(sb), _ptr(out),
+                                      _c_int64(a.numel()), _stream()), "scaled_sum2")
     return out

@@ -1,5 +1,5 @@
 """Parts a layer is put together from, and their registries."""
-from . import (attention, block, diff_attention, embedding, ffn, latent_attention, linear_recurrence, moe, norm,  # noqa: F401
+from . import (attention, block, diff_attention, embedding, ffn, latent_attention, linear_recurrence, matrix_memory, moe, norm,  # noqa: F401
                normed_attention, parallel, position, recurrent)  # noqa: F401  (register the built-in parts)
 from .base import BuildContext, KVRequest, ResidualStream, StateRequest
 from .registry import (arrangement_class, embedding_class, feed_forward_class, head_class, mixer_class, norm_class,

@@ -44,13 +44,15 @@ class KVRequest:
     compressed value.  ``values_in_keys``: there is no pool of values; a mixer whose values are part of what it
     keeps as keys (one latent row per token) gets the key pool as both.  ``chunk`` > 0: a query sees only the keys
     of its own block of ``chunk`` positions (counted from the sequence's start), so the cache gives back the pages
-    that lie wholly before the block of the next position."""
+    that lie wholly before the block of the next position.  ``keep_first`` > 0 (with a window): the keys at positions
+    below it stay visible to every later query, so their pages are never given back."""
     kv_heads: int
     head_dim: int
     window: int = 0
     value_dim: int = 0
     values_in_keys: bool = False
     chunk: int = 0
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

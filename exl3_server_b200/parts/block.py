@@ -20,6 +20,15 @@ float32, and the two norms that the next block of this kind applies to the new r
 (``kernels.tanh_norm_add``) when those norms are of the ``tanh`` kind; other norms run as kernels of their own.  The
 vectors are tensors of the arrangement (names under ``mixer_scale`` and ``feed_forward_scale``).  A layer may have no
 feed-forward.
+
+``hyper``: hyper-connections.  The residual is ``streams`` rows per token, ``x_1 .. x_S``, all equal to the embedding at
+the start.  Sublayer q (1: the mixer, 2: the feed-forward) reads ``u = sum_s a_q[s] x_s``, runs on ``norm_q(u)`` and
+writes to every stream at once from the old ones, ``x_t <- sum_s M_q[s, t] x_s + b_q[t] y`` (``M_q`` indexed [from,
+to]).  ``a_q``, ``b_q`` and ``M_q`` are tensors of the arrangement (names under ``hyper1`` / ``hyper2`` + ``.in``,
+``.out``, ``.mix``).  A write and the read that follows it (the next sublayer's, or the next block's first) are one
+float32 kernel (``kernels.hyper_step``), so a layer has as many element-wise kernels as a pre-norm layer has.  With
+one stream, ``M = [[1]]`` and ``a = b = [1]`` this is ``prenorm``.  The model's last norm must be of the
+``rms_streams`` kind (it sums the streams).  A layer may have no feed-forward.
 """
 from __future__ import annotations
 
@@ -193,7 +202,88 @@ class SideBySideBlock:
             (2 if self.feed_forward_scale is not None else 1)
 
 
+class HyperBlock:
+    takes_tensors = True      # built with the checkpoint's tensors (read, write and mixing weights of the streams)
+    takes_next = True         # forward gets the block that runs next
+
+    @classmethod
+    def tensor_specs(cls, spec: LayerSpec) -> List[TensorSpec]:
+        S = int(spec.params.get("streams", 1))
+        out = []
+        for key in ("hyper1", "hyper2") if spec.feed_forward is not None else ("hyper1",):
+            n = spec.names[key]
+            out += [TensorSpec(n + ".in", (S,), init="ones"), TensorSpec(n + ".out", (S,), init="ones"),
+                    TensorSpec(n + ".mix", (S, S))]
+        return out
+
+    def __init__(self, spec: LayerSpec, mixer, feed_forward, mixer_norm, feed_forward_norm,
+                 tensors: Dict[str, torch.Tensor]):
+        if spec.residual_scale != 1.0:
+            raise ValueError("hyper: the write weights are the scale of a sublayer's output")
+        self.spec = spec
+        self.streams = int(spec.params.get("streams", 1))
+        if not 1 <= self.streams <= K.hyper_max_streams():
+            raise ValueError(f"hyper: {self.streams} streams (1 to {K.hyper_max_streams()})")
+        self.mixer = mixer
+        self.feed_forward = feed_forward              # None: the layer is its mixer only
+        self.mixer_norm = mixer_norm
+        self.feed_forward_norm = feed_forward_norm if feed_forward is not None else None
+        for n in (self.mixer_norm, self.feed_forward_norm):
+            if n is not None and not hasattr(n, "weight"):
+                raise ValueError("hyper: the sublayers' norms must be RMS norms with a weight")
+        get = lambda name: tensors[name].float().contiguous()
+        self.read1, self.write1, self.mix1 = (get(spec.names["hyper1"] + s) for s in (".in", ".out", ".mix"))
+        self.read2 = self.write2 = self.mix2 = None
+        if feed_forward is not None:
+            self.read2, self.write2, self.mix2 = (get(spec.names["hyper2"] + s) for s in (".in", ".out", ".mix"))
+
+    def first_read(self):
+        """``(read weights, norm)`` of this block's first sublayer, for the block before it."""
+        return self.read1, self.mixer_norm
+
+    def _step(self, stream: ResidualStream, y, mix, write, nxt):
+        """Writes ``y`` into the streams and reads for ``nxt`` = (read weights, norm) or None."""
+        read, norm = nxt if nxt is not None else (None, None)
+        _, r = K.hyper_step(stream.h, self.streams, y, mix, write, read, norm.weight if norm is not None else None,
+                            norm.spec.eps if norm is not None else 0.0,
+                            norm.out_dtype if norm is not None else torch.float32)
+        return r
+
+    def forward(self, stream: ResidualStream, batch, kv, state, next_block=None) -> None:
+        S, W = self.streams, self.spec.mixer.width
+        if stream.pending is not None:
+            raise RuntimeError("hyper: the residual stream holds an output that was not folded in")
+        left = stream.take_for((self.mixer_norm,))
+        if left is not None:
+            r = left[0]
+        elif stream.h.shape[1] == W and S > 1:
+            # the embedding's single row stands for S equal streams: the first read also widens it
+            wide = torch.empty((stream.h.shape[0], S * W), dtype=torch.float32, device=stream.h.device)
+            _, r = K.hyper_step(stream.h, S, None, None, None, self.read1, self.mixer_norm.weight,
+                                self.mixer_norm.spec.eps, self.mixer_norm.out_dtype, out=wide)
+            stream.h = wide
+        else:
+            r = self._step(stream, None, None, None, self.first_read())
+        stream.act = None
+        y = self.mixer.forward(r, batch, kv, state)
+        nxt = next_block.first_read() if hasattr(next_block, "first_read") else None
+        if self.feed_forward is not None:
+            r = self._step(stream, y, self.mix1, self.write1, (self.read2, self.feed_forward_norm))
+            y = self.feed_forward.forward(r, batch)
+            r = self._step(stream, y, self.mix2, self.write2, nxt)
+        else:
+            r = self._step(stream, y, self.mix1, self.write1, nxt)
+        stream.normed = None
+        if nxt is not None:
+            stream.leave_for((nxt[1],), [r])
+
+    def weight_bytes(self) -> int:
+        return sum(p.weight_bytes() for p in (self.mixer, self.feed_forward, self.mixer_norm, self.feed_forward_norm)
+                   if p is not None and hasattr(p, "weight_bytes"))
+
+
 register_arrangement("prenorm", PreNormBlock)
+register_arrangement("hyper", HyperBlock)
 register_arrangement("side_by_side", SideBySideBlock)
 register_arrangement("sandwich", SandwichBlock)
 register_arrangement("outnorm", OutNormBlock)

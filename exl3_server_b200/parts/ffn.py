@@ -6,7 +6,7 @@ up projections are one fused matrix; the product ``silu(g) * u`` is float32
 inside its kernel.
 
 ``dense``: ``y = act(r Wu^T) Wd^T`` with an activation named in the spec's
-``params["activation"]``: ``xielu``, ``gelu`` (exact, by erf) or ``gelu_tanh``.  ``xielu`` has two learned numbers ``p, q`` (tensor
+``params["activation"]``: ``xielu``, ``gelu`` (exact, by erf), ``gelu_tanh`` or ``relu2`` (the square of relu).  ``xielu`` has two learned numbers ``p, q`` (tensor
 ``act``): ``softplus(p) z^2 + z/2`` for ``z > 0`` and
 ``(1/2 + softplus(q)) (exp(z) - 1 - z) + z/2`` otherwise; it is computed in
 float32 (from float32 results of the up projection where the projection's kernel has them); for steps of few
@@ -15,6 +15,9 @@ tokens it is the epilogue of the up projection's weight-streaming kernel.
 ``gated``: ``y = Wd (act(Wg r) * (Wu r))`` with the gate's activation named in ``params["activation"]`` (``silu``,
 ``gelu`` or ``gelu_tanh``); tensors ``gate``, ``up``, ``down``.  Gate and up are one matrix; the product is float32
 inside its kernel.
+
+``clamped_glu``: ``y = Wd (g sigmoid(alpha g) (u + 1))`` with ``g = min(Wg r, limit)`` and ``u = clamp(Wu r, -limit,
+limit)``; parameters ``limit`` and ``alpha`` (1.702 unless given); tensors ``gate``, ``up``, ``down``, no biases.
 """
 from __future__ import annotations
 
@@ -102,6 +105,14 @@ def _gelu_tanh(z: torch.Tensor, tensors, out_dtype):
     return K.activation(z, out_dtype, "gelu_tanh")
 
 
+def _relu2(z: torch.Tensor, tensors, out_dtype):
+    return K.activation(z, out_dtype, "relu2")
+
+
+def _relu2_fused(linear: Linear, x: torch.Tensor, tensors, out_dtype):
+    return linear.gelu(x, out_dtype, relu2=True)
+
+
 def _gelu_fused(linear: Linear, x: torch.Tensor, tensors, out_dtype):
     return linear.gelu(x, out_dtype, tanh=False)
 
@@ -119,7 +130,8 @@ def _no_prepare(tensors) -> None:
 #          function({suffix: tensor}) called once when the part is built)
 ACTIVATIONS = {"xielu": ((("act", (2,)),), _xielu, _xielu_fused, _xielu_prepare),
                "gelu": ((), _gelu, _gelu_fused, _no_prepare),             # z/2 (1 + erf(z / sqrt 2))
-               "gelu_tanh": ((), _gelu_tanh, _gelu_tanh_fused, _no_prepare)}   # z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+               "gelu_tanh": ((), _gelu_tanh, _gelu_tanh_fused, _no_prepare),   # z/2 (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))
+               "relu2": ((), _relu2, _relu2_fused, _no_prepare)}               # max(z, 0)^2
 
 
 class DenseFeedForward:
@@ -182,6 +194,35 @@ class GatedFeedForward:
         return self.gate_up.weight_bytes() + self.down.weight_bytes()
 
 
+class ClampedGLU:
+    ALPHA = 1.702
+
+    @staticmethod
+    def tensor_specs(spec: FeedForwardSpec, prefix: str) -> List[TensorSpec]:
+        return [TensorSpec(prefix + "gate", (spec.inner, spec.width)), TensorSpec(prefix + "up", (spec.inner, spec.width)),
+                TensorSpec(prefix + "down", (spec.width, spec.inner))]
+
+    def __init__(self, spec: FeedForwardSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
+        self.spec = spec
+        self.dtype = ctx.dtype
+        self.limit = float(spec.params["limit"])
+        self.alpha = float(spec.params.get("alpha", self.ALPHA))
+        if not self.limit > 0:
+            raise ValueError("clamped glu: the limit must be positive")
+        self.gate_up = Linear(torch.cat([tensors[prefix + "gate"].to(ctx.dtype), tensors[prefix + "up"].to(ctx.dtype)],
+                                        dim=0), None, ctx.dtype)
+        self.down = Linear(tensors[prefix + "down"], None, ctx.dtype)
+
+    def forward(self, x: torch.Tensor, batch) -> torch.Tensor:
+        T = x.shape[0]
+        gu = self.gate_up(x, out_dtype=self.gate_up.wide_dtype(T))
+        return self.down(K.clamped_glu(gu, self.limit, self.alpha, self.dtype), out_dtype=self.down.wide_dtype(T))
+
+    def weight_bytes(self) -> int:
+        return self.gate_up.weight_bytes() + self.down.weight_bytes()
+
+
 register_feed_forward("swiglu", SwiGLU)
+register_feed_forward("clamped_glu", ClampedGLU)
 register_feed_forward("gated", GatedFeedForward)
 register_feed_forward("dense", DenseFeedForward)

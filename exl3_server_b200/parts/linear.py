@@ -147,12 +147,12 @@ class Linear:
             return None
         return K.gemv_bf16_act(x, self.weight, self.bias, out_dtype, act_p, act_n)
 
-    def gelu(self, x: torch.Tensor, out_dtype: torch.dtype, tanh: bool = False) -> Optional[torch.Tensor]:
-        """The projection with GELU (exact, or by the tanh formula) in its own epilogue, where the kernel that takes
-        these rows has it (the weight-streaming GEMV); else None."""
+    def gelu(self, x: torch.Tensor, out_dtype: torch.dtype, tanh: bool = False, relu2: bool = False) -> Optional[torch.Tensor]:
+        """The projection with GELU (exact, or by the tanh formula; ``relu2``: the square of relu instead) in its own
+        epilogue, where the kernel that takes these rows has it (the weight-streaming GEMV); else None."""
         if isinstance(x, RawNormed) or self._streaming_kernel(x.shape[0]) is not K.gemv_bf16_normed:
             return None
-        return K.gemv_bf16_gelu(x, self.weight, self.bias, out_dtype, tanh=tanh)
+        return K.gemv_bf16_gelu(x, self.weight, self.bias, out_dtype, tanh=tanh, relu2=relu2)
 
     def streams_weights(self, rows: int) -> bool:
         """Whether ``rows`` rows of input go through a kernel that reads the weights once."""

@@ -12,6 +12,9 @@ Parameters of the spec: ``suffix`` (the tensor's name after the prefix), ``one_p
 around zero and the factor is ``1 + w``) and ``scale`` (a constant on the norm's output, such as a multiplier of
 the residual branch).
 
+``rms_streams``: the RMS norm of a residual of several streams (``params["streams"]``, see ``parts/block.py``,
+arrangement ``hyper``): the streams are summed and the sum is normed, in one kernel.
+
 ``tanh``: a norm that computes no statistics, ``r = tanh(alpha * h) * w + b`` with one learned number ``alpha`` and
 the vectors ``w`` and ``b`` (tensors: the prefix itself, or prefix + ``suffix``, for ``w``; that name + ``.b`` and
 + ``.alpha``).  Float32 throughout.  The spec's ``eps`` is not used.
@@ -98,6 +101,35 @@ class RMSNorm:
         return self.weight.numel() * self.weight.element_size()
 
 
+class StreamsRMSNorm(RMSNorm):
+    """``r = rmsnorm(sum_s x_s) * w`` over a residual ``[T, streams * width]`` (or ``[T, width]``, when nothing has
+    widened it yet: equal streams)."""
+
+    offers_raw = False
+
+    def __init__(self, spec: NormSpec, tensors: Dict[str, torch.Tensor], prefix: str, ctx: BuildContext):
+        super().__init__(spec, tensors, prefix, ctx)
+        self.streams = int(spec.params.get("streams", 1))
+        self._ones = torch.ones(self.streams, dtype=torch.float32, device=self.weight.device)
+
+    def add_norm(self, stream: ResidualStream, rows: Optional[torch.Tensor] = None, out_scale: float = 1.0,
+                 raw_ok: bool = False):
+        if out_scale != 1.0 or stream.pending is not None:
+            raise ValueError("streams norm: no constant on the output and nothing pending in the stream")
+        S, W = self.streams, self.spec.width
+        if stream.h.shape[1] == W and S > 1:
+            # equal streams: their sum is S times the row; the norm of a multiple differs from the row's own only
+            # through eps, so the factor goes in as the read weights
+            ones = self._ones
+            wide = torch.empty((stream.h.shape[0], S * W), dtype=torch.float32, device=stream.h.device)
+            _, r = K.hyper_step(stream.h, S, None, None, None, ones, self.weight, self.spec.eps, self.out_dtype, out=wide)
+            if rows is not None:
+                r = r.index_select(0, rows.long())
+            return r
+        return K.hyper_step(stream.h, S, None, None, None, self._ones, self.weight, self.spec.eps, self.out_dtype,
+                            rows=rows)[1]
+
+
 class DynamicTanhNorm:
     @staticmethod
     def _name(spec: NormSpec, prefix: str) -> str:
@@ -144,4 +176,5 @@ class DynamicTanhNorm:
 
 
 register_norm("rms", RMSNorm)
+register_norm("rms_streams", StreamsRMSNorm)
 register_norm("tanh", DynamicTanhNorm)

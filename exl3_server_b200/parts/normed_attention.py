@@ -10,7 +10,12 @@ Per token ``q, k, v = r Wq^T, r Wk^T, r Wv^T`` (one joint matrix; biases optiona
 * ``v_mix``: ``"source"`` leaves this layer's values (before any mixing) for later layers of the same
   ``v_mix_key``; ``"mix"`` replaces ``v`` by ``(1 - lambda) v + lambda v_source`` with a learned scalar; the mixed
   values are what the cache keeps;
-* ``sink``: one added to the softmax's denominator (a key of score 0 without a value);
+* ``sink``: one added to the softmax's denominator (a key of score 0 without a value); ``"learned"``: the sink's
+  score is a learned number per query head (tensor ``sink``), neither scaled nor capped: ``exp(sink_h)`` is added;
+* ``window`` of the spec > 0: a query sees the last ``window`` keys, and with ``keep_first`` > 0 also the keys at
+  positions below ``keep_first`` (at their true positions);
+* ``softcap`` > 0: the scaled scores become ``softcap * tanh(score / softcap)``;
+* ``bias``: ``True`` (q, k, v and o have biases) or ``"qkv"`` (the output projection has none);
 * ``chunk`` > 0: a query sees only the causal keys of its own block of ``chunk`` positions (counted from the
   sequence's start, however the prompt was cut);
 * ``softmax_scale`` of the spec multiplies the scores.
@@ -63,7 +68,11 @@ class NormedAttention:
                TensorSpec(prefix + "v", (G * dv, spec.width)), TensorSpec(prefix + "o", (spec.width, H * dv))]
         if spec.params.get("bias", False):
             out += [TensorSpec(prefix + "q.b", (H * d,)), TensorSpec(prefix + "k.b", (G * d,)),
-                    TensorSpec(prefix + "v.b", (G * dv,)), TensorSpec(prefix + "o.b", (spec.width,))]
+                    TensorSpec(prefix + "v.b", (G * dv,))]
+            if spec.params["bias"] != "qkv":
+                out.append(TensorSpec(prefix + "o.b", (spec.width,)))
+        if spec.params.get("sink") == "learned":
+            out.append(TensorSpec(prefix + "sink", (H,)))
         if spec.params.get("qk_norm", "none") == "weight":
             out += [TensorSpec(prefix + "q.norm", (d,), init="ones"), TensorSpec(prefix + "k.norm", (d,), init="ones")]
         if spec.params.get("v_mix") in ("source", "mix"):
@@ -81,7 +90,13 @@ class NormedAttention:
         self.norm = NORM_CODES[p.get("qk_norm", "none")]
         self.eps = float(p.get("norm_eps", 1e-6))
         self.sink = bool(p.get("sink", False))
+        self.sink_vals = tensors[prefix + "sink"].float().contiguous() if p.get("sink") == "learned" else None
         self.chunk = int(p.get("chunk", 0))
+        self.window = int(spec.window)
+        self.keep_first = int(p.get("keep_first", 0)) if self.window > 0 else 0
+        self.softcap = float(p.get("softcap", 0.0) or 0.0)
+        if self.window < 0 or self.keep_first < 0 or self.softcap < 0:
+            raise ValueError("normed attention: window, keep_first and softcap must not be negative")
         self.v_mix = p.get("v_mix")
         self.v_mix_key = ("v_mix", p.get("v_mix_key", 0))
         self.scale = spec.softmax_scale if spec.softmax_scale is not None else d ** -0.5
@@ -93,7 +108,7 @@ class NormedAttention:
         wo = tensors[prefix + "o"].to(ctx.dtype)
         if self.dv_pad != dv:                               # the attention's rows are padded: zero columns for the pad
             wo = torch.nn.functional.pad(wo.view(spec.width, H, dv), (0, self.dv_pad - dv)).reshape(spec.width, -1)
-        self.o = Linear(wo, tensors[prefix + "o.b"] if bias else None, ctx.dtype)
+        self.o = Linear(wo, tensors[prefix + "o.b"] if bias and p["bias"] != "qkv" else None, ctx.dtype)
         self.q_w = tensors[prefix + "q.norm"].float().contiguous() if self.norm == 2 else None
         self.k_w = tensors[prefix + "k.norm"].float().contiguous() if self.norm == 2 else None
         self.lam = tensors[prefix + "vmix"].float().reshape(1).contiguous() if self.v_mix == "mix" else None
@@ -105,13 +120,16 @@ class NormedAttention:
         self._cuts = Attention.__new__(Attention)
         self._cuts.spec = MixerSpec(kind="attention", width=spec.width, heads=H, kv_heads=G, head_dim=self.d_pad,
                                     window=self.chunk)
+        # what the tensor-core kernels do not apply
+        self._plain_scores = self.window == 0 and self.softcap == 0.0 and self.sink_vals is None
 
     # -- what a part that projects for several mixers at once needs -----------------------------------------------
     def input_weight(self) -> Tuple[torch.Tensor, Optional[torch.Tensor]]:
         return self._w, self._b
 
     def cache_request(self) -> Optional[KVRequest]:
-        return KVRequest(self.G, self.d_pad, 0, self.dv_pad if self.dv_pad != self.d_pad else 0, chunk=self.chunk)
+        return KVRequest(self.G, self.d_pad, self.window, self.dv_pad if self.dv_pad != self.d_pad else 0, chunk=self.chunk,
+                         keep_first=self.keep_first)
 
     def state_request(self) -> Optional[StateRequest]:
         return None
@@ -157,14 +175,15 @@ class NormedAttention:
         if n > 1:
             scratch = batch.workspace.floats(K.attn_tokens_scratch_bytes(T, H, self.dv_pad, n) // 4)
         K.attn_tokens_ex(q, q.stride(0), out, kv.k, kv.v, kv.block_table, batch.tok_pos, batch.tok_seq, T, H, G,
-                         self.d_pad, self.dv_pad, kv.page_size, 0, self.chunk, self.sink, self.scale, split, n, scratch)
+                         self.d_pad, self.dv_pad, kv.page_size, self.window, self.chunk, self.sink, self.scale, split, n,
+                         scratch, keep_first=self.keep_first, softcap=self.softcap, sink_vals=self.sink_vals)
         return self.o(out, out_dtype=self.o.wide_dtype(T))
 
     def _tensor_cores(self, q: torch.Tensor, out: torch.Tensor, batch, kv) -> bool:
         """bfloat16 with keys and values of 64 or 128 features: prompts through the tcgen05 kernel, steps of few
         tokens through the kernel that streams pages by TMA, both with the sink and the blocks of positions as
         parameters.  False when the sizes are not theirs (the CUDA-core kernel then takes the step)."""
-        if self.ctx.dtype != torch.bfloat16 or self.d_pad != self.dv_pad or self.d_pad != self.d:
+        if self.ctx.dtype != torch.bfloat16 or self.d_pad != self.dv_pad or self.d_pad != self.d or not self._plain_scores:
             return False
         H, G, d, T = self.H, self.G, self.d, q.shape[0]
         if batch.max_new > 1 and batch.tiles and K.attn_prefill_tc_supported(torch.bfloat16, d, kv.page_size):
@@ -195,6 +214,9 @@ class NormedAttention:
         n = (max_kv_len + split - 1) // split
         if self.chunk > 0:
             n = min(n, (self.chunk + split - 2) // split + 1)
+        if self.window > 0:
+            # the pieces a window can touch, and those of the kept first keys before them
+            n = min(n, (self.window + split - 2) // split + 1 + (self.keep_first + split - 1) // split)
         return max(1, n)
 
     def weight_bytes(self) -> int:

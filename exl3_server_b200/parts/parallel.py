@@ -6,6 +6,9 @@ The branches are any registered mixers (``params["branches"]``: two ``MixerSpec`
 tensor-name prefixes under this mixer's; ``params["out_names"]``: the names of the two norm weights).  At most one
 branch may ask for keys and values and at most one for per-sequence state: a schedule entry has one of each.
 
+With ``params["combine"] = "weighted"`` the branches' outputs are not normed: ``y = sa * a(r) + sb * b(r)`` with the
+two constants ``params["scales"]`` (one float32 kernel, ``kernels.scaled_sum2``; no ``out_names`` then).
+
 When both branches can run on a slice of a projection (``input_weight`` / ``forward_projected``), their input
 matrices are one matrix and the step reads ``r`` once.  The norms and the sum are one float32 kernel
 (``kernels.normed_sum2``).
@@ -27,9 +30,13 @@ from .spec import MixerSpec
 class ParallelMixer:
     @staticmethod
     def _parts(spec: MixerSpec):
-        branches, prefixes, outs = spec.params["branches"], spec.params["prefixes"], spec.params["out_names"]
-        if len(branches) != 2 or len(prefixes) != 2 or len(outs) != 2:
+        branches, prefixes = spec.params["branches"], spec.params["prefixes"]
+        weighted = spec.params.get("combine", "normed_mean") == "weighted"
+        outs = [] if weighted else spec.params["out_names"]
+        if len(branches) != 2 or len(prefixes) != 2 or len(outs) != (0 if weighted else 2):
             raise ValueError("parallel mixer: two branches, two prefixes and two output-norm names")
+        if weighted and len(spec.params.get("scales", ())) != 2:
+            raise ValueError("parallel mixer: a weighted sum needs two scales")
         return branches, prefixes, outs
 
     @classmethod
@@ -46,7 +53,9 @@ class ParallelMixer:
         self.coef = float(spec.params.get("coef", 0.5))
         self.eps = float(spec.params.get("norm_eps", 1e-6))
         self.a, self.b = (mixer_class(b.kind)(b, tensors, prefix + p, ctx) for b, p in zip(branches, prefixes))
-        self.wa, self.wb = (tensors[prefix + n].float().contiguous() for n in outs)
+        self.scales = tuple(float(s) for s in spec.params["scales"]) if not outs else None
+        if outs:
+            self.wa, self.wb = (tensors[prefix + n].float().contiguous() for n in outs)
         if sum(m.cache_request() is not None for m in (self.a, self.b)) > 1 or \
                 sum(m.state_request() is not None for m in (self.a, self.b)) > 1:
             raise ValueError("parallel mixer: at most one branch with keys and values and one with state")
@@ -71,11 +80,17 @@ class ParallelMixer:
     def forward(self, x: torch.Tensor, batch, kv, state) -> torch.Tensor:
         if self.joint is not None:
             proj = self.joint(x, out_dtype=self.joint.wide_dtype(x.shape[0]))
-            ya = self.a.forward_projected(proj, 0, batch, kv, state)
-            yb = self.b.forward_projected(proj, self.split, batch, kv, state)
+            # a branch that also reads the input itself (low-rank side projections) says so
+            extra = lambda m: {"x": x} if getattr(m, "wants_input", False) else {}
+            ya = self.a.forward_projected(proj, 0, batch, kv, state, **extra(self.a))
+            yb = self.b.forward_projected(proj, self.split, batch, kv, state, **extra(self.b))
         else:
             ya = self.a.forward(x, batch, kv, state)
             yb = self.b.forward(x, batch, kv, state)
+        if self.scales is not None:
+            if ya.dtype != yb.dtype:
+                ya, yb = ya.float(), yb.float()
+            return K.scaled_sum2(ya, yb, self.scales[0], self.scales[1])
         return K.normed_sum2(ya, yb, self.wa, self.wb, self.eps, self.coef)
 
     def weight_bytes(self) -> int:

@@ -71,6 +71,8 @@ class LayerSpec:
     # (names under "mixer_out_norm" / "feed_forward_out_norm")
     mixer_out_norm: Optional[NormSpec] = None
     feed_forward_out_norm: Optional[NormSpec] = None
+    # what else the arrangement needs to know (``hyper``: the number of streams)
+    params: Dict[str, Any] = field(default_factory=dict, hash=False, compare=False)
 
 
 @dataclass(frozen=True)
