@@ -29,7 +29,9 @@ the size tables and prints a short JSON line (for profiling small cases).
 dense xIELU layers) and the Nikodra decoder (attention with a sink, attention in
 blocks beside retention, wkv recurrences, dense GELU layers) and the Nibelix
 decoder (lightning recurrences, differential attention over a window, dense and
-routed feed-forwards) beside the Llama-family decoder at equal width, depth, head count and feed-forward width,
+routed feed-forwards) and the Potodra decoder (a residual of four streams, attention over a window that keeps the first
+keys, matrix memories with exponential gates, a gated delta rule beside causal attention, dense and routed
+feed-forwards) beside the Llama-family decoder at equal width, depth, head count and feed-forward width,
 with random weights: one prompt of
 ``--prefill-tokens`` tokens and decode steps at ``--batch`` and ``--context``,
 for each of the size pairs in ``DESIGN_SIZES`` (or the one named by
@@ -169,6 +171,29 @@ def nibelix_config(z):
     layers = [NibelixLayer(kinds[i % 4][0], dict(kinds[i % 4][1]), dict(kinds[i % 4][2])) for i in range(z["layers"])]
     return NibelixConfig(vocab=z["vocab"], width=z["width"], norm_eps=1e-6, residual_mult=0.5, logit_softcap=30.0,
                          layers=layers)
+
+
+def potodra_config(z):
+    """Potodra at one of the size pairs: four streams; layers repeat attention + routed, matrix memory with exponential
+    gates + dense, causal attention beside a gated delta rule + dense, matrix memory + routed.  The attention layers have
+    the other sides' heads over a window of 1,024 positions that keeps the first 64 keys, capped scores and a sink per
+    head; the causal attention has the same heads; the recurrences' states are 64 x head_dim per head (the Nikodra and
+    Nibelix sides' recurrences have the same), the delta rule with convolutions of 4 taps; 16 experts in 4 groups of
+    which 2 are kept, 2 picks a token, experts and the shared expert a quarter of the dense feed-forward's width."""
+    from exl3_server_b200.config.potodra import PotodraConfig, PotodraLayer
+    hd = z["head_dim"]
+    plain = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": hd, "vdim": hd, "scale": hd ** -0.5,
+             "rot": {"base": 500000.0, "dims": hd}, "softcap": None, "mask": None}
+    att = dict(plain, softcap=30.0, mask={"size": 1024, "keep_first": 64})
+    memory = {"heads": z["heads"], "dim": 64, "vdim": hd, "gate_cap": 15.0}
+    delta = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": 64, "vdim": hd, "conv": 4}
+    par = {"left": plain, "right": delta, "left_scale": 0.6, "right_scale": 0.5}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4, "limit": 7.0}, "shared": {"ff": z["ff"] // 4, "limit": 7.0},
+           "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}}}
+    kinds = [("attention", att, moe), ("mlstm", memory, dense), ("parallel", par, dense), ("mlstm", memory, moe)]
+    layers = [PotodraLayer(kinds[i % 4][0], dict(kinds[i % 4][1]), dict(kinds[i % 4][2])) for i in range(z["layers"])]
+    return PotodraConfig(vocab=z["vocab"], width=z["width"], streams=4, norm_eps=1e-6, embedding_scale=2.0, layers=layers)
 
 
 def design_configs(name: str):
@@ -396,7 +421,7 @@ class Rig:
 
 
 def designs(args) -> int:
-    """``--only designs``: prefill and decode throughput of the Rigitar, Nikodra and Nibelix decoders beside the Llama-family
+    """``--only designs``: prefill and decode throughput of the Rigitar, Nikodra, Nibelix and Potodra decoders beside the Llama-family
     decoder of equal sizes; one JSON line."""
     import torch
     torch.cuda.set_device(0)
@@ -410,7 +435,8 @@ def designs(args) -> int:
     for name in ([args.design_sizes] if args.design_sizes else sorted(DESIGN_SIZES)):
         rig_cfg, llama_cfg = design_configs(name)
         rec = {}
-        for arch, cfg in (("nibelix", nibelix_config(DESIGN_SIZES[name])), ("nikodra", nikodra_config(DESIGN_SIZES[name])),
+        for arch, cfg in (("potodra", potodra_config(DESIGN_SIZES[name])), ("nibelix", nibelix_config(DESIGN_SIZES[name])),
+                          ("nikodra", nikodra_config(DESIGN_SIZES[name])),
                           ("rigitar", rig_cfg), ("llama", llama_cfg)):
             if args.design_arch not in ("both", arch):
                 continue
@@ -452,7 +478,7 @@ def main() -> int:
                     help="run one part only (for profiling small cases); prints a short JSON line")
     ap.add_argument("--design-sizes", choices=sorted(DESIGN_SIZES), default=None,
                     help="with --only designs: one size pair instead of all")
-    ap.add_argument("--design-arch", choices=["both", "nibelix", "nikodra", "rigitar", "llama"], default="both",
+    ap.add_argument("--design-arch", choices=["both", "potodra", "nibelix", "nikodra", "rigitar", "llama"], default="both",
                     help="with --only designs: one of the designs only (both: all of them)")
     ap.add_argument("--design-part", choices=["both", "prefill", "decode"], default="both",
                     help="with --only designs: one of the two measurements only")
