@@ -367,11 +367,11 @@ int exl3_hyper_step(const float* xin, int s_in, float* xout, int S, const void* 
 int exl3_mlstm_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, int qkv_dtype,
                     const void* zi, const void* zf, int gate_dtype, int64_t ld_gate, float cap, float q_scale,
                     float* s_state, float* n_state, float* m_state, const int* slot_ids, const int* row_start,
-                    float* out, int rows, int T, int heads, int dk, int dv, cudaStream_t stream);
+                    float* out, int rows, int T, int heads, int dk, int dv, int max_new, cudaStream_t stream);
 int exl3_delta_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, int qkv_dtype,
                     const void* zb, int zb_dtype, int64_t ld_zb, const void* za, int za_dtype, int64_t ld_za,
                     const float* a_log, const float* dt_bias, float* s_state, const int* slot_ids, const int* row_start,
-                    float* out, int rows, int T, int heads, int qk_heads, int dk, int dv, cudaStream_t stream);
+                    float* out, int rows, int T, int heads, int qk_heads, int dk, int dv, int max_new, cudaStream_t stream);
 // Short causal convolution per channel, SiLU, unit q and k heads (see matrix_memory.cu).  out float32 [T, 2 qk_heads dk +
 // v_heads dv]; state float32 [slots, channels, n_taps - 1].
 int exl3_conv_prep_max_taps();
@@ -382,4 +382,13 @@ int exl3_conv_prep(const void* x, int x_dtype, int64_t ldx, int q_off, int k_off
 // out = sa * a + sb * b element by element, float32 out.
 int exl3_scaled_sum2(const void* a, const void* b, int ab_dtype, float sa, float sb, float* out, int64_t n,
                      cudaStream_t stream);
+int exl3_attn_prefill_tc_opt(const void* q, int64_t q_row_stride, int T, void* out, const void* k_pool, const void* v_pool,
+                             int64_t n_pool_rows, const int* block_table, int bt_stride, const int* row_start,
+                             const int* row_pos0, const int* tile_seq, const int* tile_q0, int n_tiles, int nh, int nkv,
+                             int hd, int page, int window, int chunk, int sink, float scale, int variant, int keep_first,
+                             float softcap, const float* sink_vals, cudaStream_t stream);
+// y[M, N] (float32) = x[M, K] . w[N, K]^T (+ bias) for a handful of output features and many rows; x, w and bias of one
+// type, K and the pitch of x multiples of 16 bytes.
+int exl3_gemm_few_out(const void* x, int64_t ldx, const void* w, const void* bias, float* y, int in_dtype, int M, int N,
+                      int K, cudaStream_t stream);
 }

@@ -173,17 +173,38 @@ __device__ inline uint32_t fa_pack(float lo, float hi) {
 }
 
 // What a block needs to know of a tile of 128 queries.
+// Options beyond the plain causal softmax.  keep_first: with a window, the keys at positions below it stay visible.
+// cap_in > 0: a raw score s becomes tanh(s * cap_in) and is multiplied by cap_log2 (= cap * log2 e) instead of the
+// scale.  sink_vals: the sink's score per query head (natural units), or null for 0.
+struct FaOpts {
+  int keep_first;
+  float cap_in, cap_log2;
+  const float* sink_vals;
+};
+// Pages from the sequence's start that a tile walks before the pages of its window: those that hold kept first keys
+// and lie before the window's first page.
+__device__ inline int fa_kept_pages(int window, int keep_first, int page_lo) {
+  return (window > 0 && keep_first > 0) ? min((keep_first + FA_BK - 1) / FA_BK, page_lo) : 0;
+}
+// tanh by one exponential and one reciprocal: 1 - 2 / (1 + e^(2x)); good to 1e-6 absolutely.
+__device__ inline float fa_tanh(float x) {
+  float e, r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(e) : "f"(x * 2.8853900817779268f));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(1.0f + e));
+  return fmaf(-2.0f, r, 1.0f);
+}
 struct FaTile {
   int row0;        // the tile's first row of q and out
   int rows;        // its queries
   int p_first, p_last;   // their positions
-  int page_lo;     // the first page they may see
+  int page_lo;     // the first page of the window (or block of positions) they may see
+  int kept;        // pages from the sequence's start that are walked before it (kept first keys)
   int n_pages;     // pages to walk
   const int* bt;   // the sequence's page table
 };
 __device__ inline FaTile fa_tile(int tile, const int* block_table, int bt_stride, const int* row_start,
                                  const int* row_pos0, const int* tile_seq, const int* tile_q0, int window,
-                                 int chunk) {
+                                 int chunk, int keep_first) {
   FaTile t;
   const int b = tile_seq[tile], q0 = tile_q0[tile];
   const int n_new = row_start[b + 1] - row_start[b];
@@ -194,7 +215,8 @@ __device__ inline FaTile fa_tile(int tile, const int* block_table, int bt_stride
   int k_lo = (window > 0 && t.p_first - window + 1 > 0) ? t.p_first - window + 1 : 0;
   if (chunk > 0) k_lo = max(k_lo, t.p_first / chunk * chunk);    // the block of positions of the tile's first query
   t.page_lo = k_lo / FA_BK;
-  t.n_pages = t.p_last / FA_BK - t.page_lo + 1;
+  t.kept = fa_kept_pages(window, keep_first, t.page_lo);
+  t.n_pages = t.kept + t.p_last / FA_BK - t.page_lo + 1;
   t.bt = block_table + (int64_t)b * bt_stride;
   return t;
 }
@@ -210,7 +232,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
                        const int* __restrict__ row_pos0, const int* __restrict__ tile_seq,
                        const int* __restrict__ tile_q0, int n_tiles, int fold, int nh, int nkv, int window,
-                       int chunk, int sink, float scale_log2) {
+                       int chunk, int sink, float scale_log2, FaOpts opts) {
   extern __shared__ unsigned char fa_smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr int NB = FA_HD / 64;                             // boxes of 64 features (128-byte lines) in a head
@@ -236,7 +258,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int other = n_tiles - 1 - (int)blockIdx.y;
   const int n_own = (fold && other > (int)blockIdx.y) ? 2 : 1;
   auto tile_of = [&](int w) {                       // the block's first (w = 0) or second tile
-    return fa_tile(w ? other : (int)blockIdx.y, block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, window, chunk);
+    return fa_tile(w ? other : (int)blockIdx.y, block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, window, chunk,
+                   opts.keep_first);
   };
 
   if (threadIdx.x == 0) {
@@ -291,7 +314,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     auto numbers = [&](int c0) {                             // this lane's page number of the 32 from c0
       const int c = c0 + lane;
       if (c >= n_total) return 0;
-      return c >= n0 ? tb.bt[tb.page_lo + c - n0] : ta.bt[ta.page_lo + c];
+      const FaTile& tc = c >= n0 ? tb : ta;
+      const int jc = c >= n0 ? c - n0 : c;
+      return tc.bt[jc < tc.kept ? jc : tc.page_lo + jc - tc.kept];
     };
     int pgs = numbers(0), pgs_next = numbers(32);
     int copied = 0;                                          // pages whose copies were asked for
@@ -380,7 +405,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     for (int w = 0; w < n_own && ok; ++w) {
     const FaTile tw = tile_of(w);
     const int p_first = tw.p_first, p_last = tw.p_last, n_blocks = tw.n_pages, page_lo = tw.page_lo, rows = tw.rows;
+    const int kept = tw.kept;
     const int p = p_first + r;                               // this row's position
+    const float score_mul = opts.cap_in > 0.0f ? opts.cap_log2 : scale_log2;
     float m_used = -INFINITY, l_run = 0.0f;
     // The row of S_f is asked for as soon as the row of P_(f-1) is on its way into tensor memory (the first of a
     // tile: here), so that the load's latency and the store's pass together.
@@ -405,12 +432,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       // arithmetic below instead of standing in front of the store of P and the load of S.
       const bool p_free = f < 2 || fa_mbar_test(pv_done + st, ((f - 2) >> 1) & 1);
       const bool s_there = j + 1 < n_blocks && fa_mbar_test(s_full + (st ^ 1), ((f + 1) >> 1) & 1);
-      const int key0 = (page_lo + j) * FA_BK;
+      const int key0 = (j < kept ? j : page_lo + j - kept) * FA_BK;
       const bool need_mask = (key0 + FA_BK - 1 > p_first) || (window > 0 && key0 <= p_last - window) ||
                              (chunk > 0 && key0 < p_last / chunk * chunk);
       // four independent chains for the maximum (and below for the sum): the row is long and
       // a single chain would make every step wait for the one before
       // masking without branches (one test per page decides whether the page needs it at all)
+      if (opts.cap_in > 0.0f) {                              // capped scores: tanh now, the cap with the scale below
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) sr[h][c] = __float_as_uint(fa_tanh(__uint_as_float(sr[h][c]) * opts.cap_in));
+      }
       if (need_mask) {
         int lo_key = (window > 0) ? p - window : -1;          // keys <= lo_key are out of the window
         if (chunk > 0) lo_key = max(lo_key, p / chunk * chunk - 1);   // or before the query's block of positions
@@ -419,7 +452,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int key = key0 + h * 32 + c;
-            const bool dead = (key > p) | (key <= lo_key);
+            const bool dead = (key > p) | ((key <= lo_key) & (key >= opts.keep_first));   // kept first keys stay
             sr[h][c] = dead ? 0xff800000u : sr[h][c];         // -inf
           }
       }
@@ -430,7 +463,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         for (int c = 0; c < 32; c += 2)                      // two scores an instruction
           mx4[(c >> 1) & 3] = fa_max3(mx4[(c >> 1) & 3], __uint_as_float(sr[h][c]), __uint_as_float(sr[h][c + 1]));
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      mx *= scale_log2;                                      // scale > 0: max and scale commute
+      mx *= score_mul;                                       // scale > 0: max and scale commute
       // lazy rescale: move the reference maximum only when it is far behind
       const bool grow = mx > m_used + FA_RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
@@ -466,8 +499,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int c = 0; c < 32; ++c) {                         // two keys per column
-        const float e0 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c) >> 5][(2 * c) & 31]), scale_log2, -mref));
-        const float e1 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c + 1) >> 5][(2 * c + 1) & 31]), scale_log2, -mref));
+        const float e0 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c) >> 5][(2 * c) & 31]), score_mul, -mref));
+        const float e1 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c + 1) >> 5][(2 * c + 1) & 31]), score_mul, -mref));
         sum4[c & 3] += e0 + e1;
         pw[c] = fa_pack(e0, e1);
       }
@@ -486,7 +519,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (ok) {
         fa_fence_after();
         // a sink is a key of score 0 without a value: one more term in the sum, in the units of the reference maximum
-        const float inv = 1.0f / (sink ? l_run + fa_exp2(-m_used) : l_run);
+        const float inv = 1.0f / (sink ? l_run + fa_exp2((opts.sink_vals ? __ldg(opts.sink_vals + head) * 1.4426950408889634f : 0.0f) - m_used) : l_run);
         __nv_bfloat16* dst = out + ((int64_t)(tw.row0 + r) * nh + head) * FA_HD;
 #pragma unroll
         for (int h2 = 0; h2 < FA_HD / 64; ++h2) {            // 64 columns at a time (every thread reads: the load is the warp's)
@@ -543,7 +576,7 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
                         const int* __restrict__ block_table, int bt_stride, const int* __restrict__ row_start,
                         const int* __restrict__ row_pos0, const int* __restrict__ tile_seq,
                         const int* __restrict__ tile_q0, int nh, int nkv, int window, int chunk, int sink,
-                        float scale_log2) {
+                        float scale_log2, FaOpts opts) {
   extern __shared__ unsigned char fa_smem_raw[];
   unsigned char* base = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(fa_smem_raw) + 1023) & ~(uintptr_t)1023);
   constexpr uint32_t QB = fa_q_bytes(64), KVB = fa_kv_bytes(64);
@@ -570,7 +603,9 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   int k_lo = (window > 0 && p_first - window + 1 > 0) ? p_first - window + 1 : 0;
   if (chunk > 0) k_lo = max(k_lo, p_first / chunk * chunk);
   const int page_lo = k_lo / FA_BK, page_hi = p_last / FA_BK;
-  const int n_blocks = page_hi - page_lo + 1;
+  const int kept = fa_kept_pages(window, opts.keep_first, page_lo);
+  const int n_blocks = kept + page_hi - page_lo + 1;
+  const float score_mul = opts.cap_in > 0.0f ? opts.cap_log2 : scale_log2;
   const int* bt = block_table + (int64_t)b * bt_stride;
 
   if (threadIdx.x == 0) {
@@ -604,7 +639,7 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
     }
     auto load_kv = [&](int j) {
       const int st = j % F4_STAGES;
-      const int pg = bt[page_lo + j];
+      const int pg = bt[j < kept ? j : page_lo + j - kept];
       if (lane == 0) {
         fa_mbar_expect_tx(kv_full + st, 2 * KVB);
         fa_tma_2d(sK + st * KVB, &map_k, kv_full + st, 0, (pg * nkv + g) * FA_BK);
@@ -657,9 +692,15 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       fa_ld32(tmem_base + lane_addr, sr[0]);
       fa_ld32(tmem_base + lane_addr + 32, sr[1]);
       fa_wait_ld();
-      const int key0 = (page_lo + j) * FA_BK;
+      const int key0 = (j < kept ? j : page_lo + j - kept) * FA_BK;
       const bool need_mask = (key0 + FA_BK - 1 > p_first) || (window > 0 && key0 <= p_last - window) ||
                              (chunk > 0 && key0 < p_last / chunk * chunk);
+      if (opts.cap_in > 0.0f) {
+#pragma unroll
+        for (int h = 0; h < 2; ++h)
+#pragma unroll
+          for (int c = 0; c < 32; ++c) sr[h][c] = __float_as_uint(fa_tanh(__uint_as_float(sr[h][c]) * opts.cap_in));
+      }
       if (need_mask) {
         int lo_key = (window > 0) ? p - window : -1;
         if (chunk > 0) lo_key = max(lo_key, p / chunk * chunk - 1);
@@ -668,7 +709,7 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
           for (int c = 0; c < 32; ++c) {
             const int key = key0 + h * 32 + c;
-            const bool dead = (key > p) | (key <= lo_key);
+            const bool dead = (key > p) | ((key <= lo_key) & (key >= opts.keep_first));
             sr[h][c] = dead ? 0xff800000u : sr[h][c];
           }
       }
@@ -678,7 +719,7 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
 #pragma unroll
         for (int c = 0; c < 32; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], __uint_as_float(sr[h][c]));
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      mx *= scale_log2;
+      mx *= score_mul;
       const bool grow = mx > m_used + FA_RESCALE_STEP || (m_used == -INFINITY && mx > -INFINITY);
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = grow ? mx : m_used;
@@ -709,8 +750,8 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
       for (int c = 0; c < 32; ++c) {                         // two keys per column, written over the scores' registers
-        const float e0 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c) >> 5][(2 * c) & 31]), scale_log2, -mref));
-        const float e1 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c + 1) >> 5][(2 * c + 1) & 31]), scale_log2, -mref));
+        const float e0 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c) >> 5][(2 * c) & 31]), score_mul, -mref));
+        const float e1 = fa_exp2(fmaf(__uint_as_float(sr[(2 * c + 1) >> 5][(2 * c + 1) & 31]), score_mul, -mref));
         sum4[c & 3] += e0 + e1;
         sr[0][c] = fa_pack(e0, e1);
       }
@@ -725,7 +766,7 @@ attn_prefill_tc4_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       ok = fa_mbar_wait(pv_done, jl & 1);
       if (ok) {
         fa_fence_after();
-        const float inv = 1.0f / (sink ? l_run + fa_exp2(-m_used) : l_run);
+        const float inv = 1.0f / (sink ? l_run + fa_exp2((opts.sink_vals ? __ldg(opts.sink_vals + head) * 1.4426950408889634f : 0.0f) - m_used) : l_run);
         __nv_bfloat16* dst = out + ((int64_t)(row_start[b] + q0 + r) * nh + head) * 64;
 #pragma unroll 1
         for (int c0 = 0; c0 < 64; c0 += 32) {
@@ -804,12 +845,25 @@ extern "C" int exl3_attn_prefill_tc_status() {
 
 // q: rows of the fused q|k|v buffer (row stride q_row_stride elements, T rows in all); tiles of 128 queries.
 // n_pool_rows = pages * kv_heads * 64 rows of head_dim in each of k_pool and v_pool.
-extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, void* out, const void* k_pool,
-                                    const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
-                                    const int* row_start, const int* row_pos0, const int* tile_seq,
-                                    const int* tile_q0, int n_tiles, int nh, int nkv, int hd, int page, int window,
-                                    int chunk, int sink, float scale, int variant, cudaStream_t stream) {
+// The options of the general form: with a window, keys at positions below keep_first stay visible; softcap > 0 replaces a
+// scaled score s by softcap * tanh(s / softcap); sink_vals [heads] (float32, with sink) are the sink's scores.
+extern "C" int exl3_attn_prefill_tc_opt(const void* q, int64_t q_row_stride, int T, void* out, const void* k_pool,
+                                        const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
+                                        const int* row_start, const int* row_pos0, const int* tile_seq,
+                                        const int* tile_q0, int n_tiles, int nh, int nkv, int hd, int page, int window,
+                                        int chunk, int sink, float scale, int variant, int keep_first, float softcap,
+                                        const float* sink_vals, cudaStream_t stream) {
   if (n_tiles == 0) return 0;
+  if (keep_first < 0 || softcap < 0.0f || !(scale > 0.0f) || (sink_vals != nullptr && !sink)) {
+    set_error("attn_prefill_tc: keep_first %d, softcap %g, scale %g: none may be negative, and sink scores need the sink",
+              keep_first, (double)softcap, (double)scale);
+    return ERR_BAD_ARGUMENT;
+  }
+  FaOpts opts;
+  opts.keep_first = window > 0 ? keep_first : 0;
+  opts.cap_in = softcap > 0.0f ? scale / softcap : 0.0f;
+  opts.cap_log2 = softcap * 1.4426950408889634f;
+  opts.sink_vals = sink_vals;
   if (!exl3_attn_prefill_tc_supported(DT_BF16, hd, page)) {
     set_error("attn_prefill_tc: needs bfloat16, head_dim 64 or 128 and pages of 64, got head_dim %d page %d", hd, page);
     return ERR_UNSUPPORTED;
@@ -859,12 +913,22 @@ extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, 
   const float scale_log2 = scale * 1.4426950408889634f;
   if (four)
     launch_pdl(attn_prefill_tc4_kernel, grid, dim3(FA_THREADS), F4_SMEM, stream, map_q, map_k, map_v, o, block_table,
-               bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, chunk, sink, scale_log2);
+               bt_stride, row_start, row_pos0, tile_seq, tile_q0, nh, nkv, window, chunk, sink, scale_log2, opts);
   else if (hd == 64)
     launch_pdl(attn_prefill_tc_kernel<64>, grid, dim3(FA_THREADS_MAIN), fa_smem(64), stream, map_q, map_k, map_v, o,
-               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, n_tiles, fold, nh, nkv, window, chunk, sink, scale_log2);
+               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, n_tiles, fold, nh, nkv, window, chunk, sink, scale_log2, opts);
   else
     launch_pdl(attn_prefill_tc_kernel<128>, grid, dim3(FA_THREADS_MAIN), fa_smem(128), stream, map_q, map_k, map_v, o,
-               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, n_tiles, fold, nh, nkv, window, chunk, sink, scale_log2);
+               block_table, bt_stride, row_start, row_pos0, tile_seq, tile_q0, n_tiles, fold, nh, nkv, window, chunk, sink, scale_log2, opts);
   return launch_status("attn_prefill_tc");
+}
+
+extern "C" int exl3_attn_prefill_tc(const void* q, int64_t q_row_stride, int T, void* out, const void* k_pool,
+                                    const void* v_pool, int64_t n_pool_rows, const int* block_table, int bt_stride,
+                                    const int* row_start, const int* row_pos0, const int* tile_seq,
+                                    const int* tile_q0, int n_tiles, int nh, int nkv, int hd, int page, int window,
+                                    int chunk, int sink, float scale, int variant, cudaStream_t stream) {
+  return exl3_attn_prefill_tc_opt(q, q_row_stride, T, out, k_pool, v_pool, n_pool_rows, block_table, bt_stride, row_start,
+                                  row_pos0, tile_seq, tile_q0, n_tiles, nh, nkv, hd, page, window, chunk, sink, scale,
+                                  variant, 0, 0.0f, nullptr, stream);
 }

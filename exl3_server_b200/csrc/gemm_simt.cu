@@ -98,3 +98,69 @@ extern "C" int exl3_gemm_simt(const void* x, const void* w, const void* bias, vo
   set_error("gemm_simt: unsupported element types in=%d out=%d", in_dtype, out_dtype);
   return ERR_UNSUPPORTED;
 }
+
+// y[M, N] = x[M, K] . w[N, K]^T (+ bias) in float32 for a handful of output features and many rows (a few gates or
+// scores per token): a warp a row of x, the lanes striding K in 16-byte pieces, four output features at a time over
+// the same pieces of x; the row of x and the few rows of w stay in L1 and L2.  One order of summation per (row,
+// feature), whatever M.
+namespace exl3 {
+
+constexpr int FEW_WARPS = 8;
+
+template <typename T>
+__global__ void __launch_bounds__(FEW_WARPS * 32)
+gemm_few_out_kernel(const T* __restrict__ x, int64_t ldx, const T* __restrict__ w, const T* __restrict__ bias,
+                    float* __restrict__ y, int M, int N, int K) {
+  constexpr int VEC = Elem<T>::vec;
+  pdl_wait();
+  pdl_trigger();
+  const int lane = threadIdx.x & 31;
+  const int m = blockIdx.x * FEW_WARPS + (threadIdx.x >> 5);
+  if (m >= M) return;
+  const T* xr = x + (int64_t)m * ldx;
+  const int pieces = K / VEC;
+  for (int n0 = 0; n0 < N; n0 += 4) {
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int p = lane; p < pieces; p += 32) {
+      float xv[VEC];
+      load_vec_cg(xr + (int64_t)p * VEC, xv);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (n0 + u < N) {
+          float wv[VEC];
+          load_vec(w + (int64_t)(n0 + u) * K + (int64_t)p * VEC, wv);
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) acc[u] = fmaf(xv[e], wv[e], acc[u]);
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const float v = warp_sum(acc[u]);
+      if (lane == 0 && n0 + u < N) y[(int64_t)m * N + n0 + u] = v + (bias ? Elem<T>::load(bias + n0 + u) : 0.0f);
+    }
+  }
+}
+
+}  // namespace exl3
+
+extern "C" int exl3_gemm_few_out(const void* x, int64_t ldx, const void* w, const void* bias, float* y, int in_dtype,
+                                 int M, int N, int K, cudaStream_t stream) {
+  if (M == 0 || N == 0) return 0;
+  const int vec = in_dtype == DT_F32 ? 4 : 8;
+  if (M < 0 || N < 0 || K < 1 || (in_dtype != DT_F32 && in_dtype != DT_BF16) || K % vec != 0 || ldx % vec != 0 ||
+      !aligned16(x) || !aligned16(w)) {
+    set_error("gemm_few_out: needs float32 or bfloat16 inputs, K and the pitch of x in 16-byte pieces, got M=%d N=%d K=%d", M,
+              N, K);
+    return ERR_BAD_ARGUMENT;
+  }
+  const dim3 grid(ceil_div(M, FEW_WARPS));
+  if (in_dtype == DT_F32)
+    launch_pdl(gemm_few_out_kernel<float>, grid, dim3(FEW_WARPS * 32), 0, stream, static_cast<const float*>(x), ldx,
+               static_cast<const float*>(w), static_cast<const float*>(bias), y, M, N, K);
+  else
+    launch_pdl(gemm_few_out_kernel<__nv_bfloat16>, grid, dim3(FEW_WARPS * 32), 0, stream,
+               static_cast<const __nv_bfloat16*>(x), ldx, static_cast<const __nv_bfloat16*>(w),
+               static_cast<const __nv_bfloat16*>(bias), y, M, N, K);
+  return launch_status("gemm_few_out");
+}

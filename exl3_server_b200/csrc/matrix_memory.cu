@@ -16,7 +16,9 @@
 //
 // Both: a block owns some columns of S of one (row, head) and walks the row's tokens in order; a column lives in the
 // registers of four neighbouring lanes (rows i = 4 j + lane % 4), the two dot products of a token are summed inside
-// the four lanes; q, k, the decays and the token's scalars are staged in shared memory one token ahead.
+// the four lanes; q, k, the decays, the block's values and the tokens' scalars are staged in shared memory a chunk of
+// tokens at a time (the gates' exponentials of a chunk side by side, only the running maximum in order), so that a
+// token's step reads shared memory only and a chunk's load latency is paid once.
 //
 // conv_prep: per channel a causal convolution over time of `taps` taps (the last tap is the current token's), no bias,
 // zeros before the sequence's start, then SiLU; the q and k heads are then made unit vectors, x / sqrt(sum x^2 + eps),
@@ -31,14 +33,26 @@ namespace exl3 {
 constexpr int MM_LANES = 4;             // lanes that share a column
 constexpr int MM_COLS = 32;             // columns a block owns
 constexpr int MM_THREADS = MM_LANES * MM_COLS;
+constexpr int MM_CHUNK = 128;           // tokens whose vectors are staged in shared memory at once (at most MM_THREADS)
 constexpr int CONV_MAX_TAPS = 8;
-constexpr int CONV_CHUNK = 16;          // tokens a warp walks (at least CONV_MAX_TAPS - 1)
+constexpr int CONV_MIN_CHUNK = 4;       // tokens a warp walks at least
 constexpr int CONV_WARPS = 4;
 constexpr int CONV_MAX_PER_LANE = 8;    // heads of up to 256 channels
 
 __device__ inline float mm_load(const void* p, int dtype, int64_t i) {
   return dtype == DT_F32 ? __ldcg(static_cast<const float*>(p) + i)
                          : __bfloat162float(__ldcg(static_cast<const __nv_bfloat16*>(p) + i));
+}
+
+// Four consecutive elements (the address a multiple of four elements, the base 16-byte aligned).
+__device__ inline void mm_load4(const void* p, int dtype, int64_t i, float (&v)[4]) {
+  if (dtype == DT_F32) {
+    load_vec_cg(static_cast<const float*>(p) + i, v);
+  } else {
+    const uint2 r = __ldcg(reinterpret_cast<const uint2*>(static_cast<const __nv_bfloat16*>(p) + i));
+    v[0] = __uint_as_float(r.x << 16); v[1] = __uint_as_float(r.x & 0xffff0000u);
+    v[2] = __uint_as_float(r.y << 16); v[3] = __uint_as_float(r.y & 0xffff0000u);
+  }
 }
 
 __device__ inline float mm_softplus(float x) { return x > 20.0f ? x : log1pf(expf(x)); }
@@ -59,48 +73,112 @@ struct MatrixMemoryArgs {
   const int* slot_ids; const int* row_start;
   float* out;                         // [T, H * dv]
   int H, QH, dk, dv;
+  int vec;                            // q, k (and za) can be read four elements at a time
 };
 
-// Stages token t's q, k (and decays) and scalars into buffer `buf`.  sc: [0] a (decay of the state), [1] b (weight of
-// the write), [2] exp(-m'), [3] beta.  m_run is thread 0's running maximum (mode 0).
+// Stages a chunk of up to MM_CHUNK tokens from t0 on into shared memory: q (scaled) and k as [token][dk], for mode 1 the
+// decays likewise, the block's columns of v as [token][MM_COLS], and the tokens' scalars as [token][4]: mode 0
+// a = exp(f + m - m'), b = exp(i - m'), exp(-m'); mode 1 beta.  Every thread of the block takes part; the running
+// maximum m_run (mode 0) is carried by every thread alike.  Ends with a barrier.
 template <int MODE>
-__device__ inline void mm_stage(const MatrixMemoryArgs& g, int64_t t, int h, int qh, float* sq, float* sk, float* sg,
-                                float* sc, float& m_run) {
-  for (int i = threadIdx.x; i < g.dk; i += MM_THREADS) {
-    sq[i] = mm_load(g.q, g.qkv_dtype, t * g.ldq + (int64_t)qh * g.dk + i) * g.q_scale;
-    sk[i] = mm_load(g.k, g.qkv_dtype, t * g.ldk + (int64_t)qh * g.dk + i);
-    if (MODE == 1) {
-      const float za = mm_load(g.za, g.za_dtype, t * g.ld_za + (int64_t)h * g.dk + i) + __ldg(g.dt_bias + h * g.dk + i);
-      sg[i] = expf(-expf(__ldg(g.a_log + h)) * mm_softplus(za));
+__device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, int h, int qh, int j0, float* sq, float* sk,
+                                      float* sg, float* sv, float* sc, float* sgate, float& m_run) {
+  const int dk = g.dk, dv = g.dv;
+  if (g.vec) {
+    // rows of q, k (and the decays' pre-activations) in 16-byte pieces, four pieces of each in flight a thread
+    const int per = dk / 4;                           // pieces of four features in a token's row
+    const float ea = MODE == 1 ? expf(__ldg(g.a_log + h)) : 0.0f;
+    for (int e0 = threadIdx.x; e0 < n * per; e0 += MM_THREADS * 4) {
+      float vq[4][4], vk[4][4], va[4][4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = e0 + u * MM_THREADS;
+        if (e < n * per) {
+          const int tt = e / per, i = (e - tt * per) * 4;
+          const int64_t t = t0 + tt;
+          mm_load4(g.q, g.qkv_dtype, t * g.ldq + (int64_t)qh * dk + i, vq[u]);
+          mm_load4(g.k, g.qkv_dtype, t * g.ldk + (int64_t)qh * dk + i, vk[u]);
+          if (MODE == 1) mm_load4(g.za, g.za_dtype, t * g.ld_za + (int64_t)h * dk + i, va[u]);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int e = e0 + u * MM_THREADS;
+        if (e < n * per) {
+          const int tt = e / per, i = (e - tt * per) * 4;
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            sq[tt * dk + i + c] = vq[u][c] * g.q_scale;
+            sk[tt * dk + i + c] = vk[u][c];
+            if (MODE == 1) sg[tt * dk + i + c] = expf(-ea * mm_softplus(va[u][c] + __ldg(g.dt_bias + h * dk + i + c)));
+          }
+        }
+      }
+    }
+  } else {
+    for (int e = threadIdx.x; e < n * dk; e += MM_THREADS) {
+      const int tt = e / dk, i = e - tt * dk;
+      const int64_t t = t0 + tt;
+      sq[e] = mm_load(g.q, g.qkv_dtype, t * g.ldq + (int64_t)qh * dk + i) * g.q_scale;
+      sk[e] = mm_load(g.k, g.qkv_dtype, t * g.ldk + (int64_t)qh * dk + i);
+      if (MODE == 1) {
+        const float za = mm_load(g.za, g.za_dtype, t * g.ld_za + (int64_t)h * dk + i) + __ldg(g.dt_bias + h * dk + i);
+        sg[e] = expf(-expf(__ldg(g.a_log + h)) * mm_softplus(za));
+      }
     }
   }
-  if (threadIdx.x == 0) {
-    if (MODE == 0) {
-      const float zi = mm_load(g.zi, g.gate_dtype, t * g.ld_gate + h), zf = mm_load(g.zf, g.gate_dtype, t * g.ld_gate + h);
-      const float gi = g.cap * tanhf(zi / g.cap);
-      const float gf = mm_logsigmoid(g.cap * tanhf(zf / g.cap));
-      const float mn = fmaxf(gf + m_run, gi);
-      sc[0] = expf(gf + m_run - mn);
-      sc[1] = expf(gi - mn);
-      sc[2] = expf(-mn);
-      sc[4] = mn;
-      m_run = mn;
-    } else {
-      sc[3] = 1.0f / (1.0f + expf(-mm_load(g.zb, g.zb_dtype, t * g.ld_zb + h)));
-    }
+  for (int e = threadIdx.x; e < n * MM_COLS; e += MM_THREADS) {
+    const int tt = e / MM_COLS, c = e - tt * MM_COLS;
+    sv[e] = (j0 + c < dv) ? mm_load(g.v, g.qkv_dtype, (int64_t)(t0 + tt) * g.ldv + (int64_t)h * dv + j0 + c) : 0.0f;
   }
+  if (MODE == 1) {
+    if (threadIdx.x < n)
+      sc[threadIdx.x * 4 + 3] = 1.0f / (1.0f + expf(-mm_load(g.zb, g.zb_dtype, (int64_t)(t0 + threadIdx.x) * g.ld_zb + h)));
+    __syncthreads();
+    return;
+  }
+  // mode 0: the gates of the chunk's tokens side by side, then the running maximum in order, then the three factors
+  if (threadIdx.x < n) {
+    const int64_t t = t0 + threadIdx.x;
+    const float zi = mm_load(g.zi, g.gate_dtype, t * g.ld_gate + h), zf = mm_load(g.zf, g.gate_dtype, t * g.ld_gate + h);
+    sgate[2 * threadIdx.x] = g.cap * tanhf(zi / g.cap);
+    sgate[2 * threadIdx.x + 1] = mm_logsigmoid(g.cap * tanhf(zf / g.cap));
+  }
+  __syncthreads();
+  // every thread walks the maxima itself (a few instructions a token, no exponentials): all hold the same m_run
+  float m = m_run;
+  float m_before = m, m_after = m;
+  for (int tt = 0; tt < n; ++tt) {
+    const float mn = fmaxf(sgate[2 * tt + 1] + m, sgate[2 * tt]);
+    if (tt == (int)threadIdx.x) { m_before = m; m_after = mn; }
+    m = mn;
+  }
+  m_run = m;
+  if (threadIdx.x < n) {
+    const float gi = sgate[2 * threadIdx.x], gf = sgate[2 * threadIdx.x + 1];
+    sc[threadIdx.x * 4 + 0] = expf(gf + m_before - m_after);
+    sc[threadIdx.x * 4 + 1] = expf(gi - m_after);
+    sc[threadIdx.x * 4 + 2] = expf(-m_after);
+  }
+  __syncthreads();
 }
 
 // NR: rows of a column that one lane holds (dk <= 4 NR).
 template <int MODE, int NR>
-__global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(MatrixMemoryArgs g) {
-  extern __shared__ float sm[];                      // two buffers of [q | k | g] (dk each) and 8 scalars
+__global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(MatrixMemoryArgs g, int chunk) {
+  extern __shared__ float sm[];                      // q, k, (g) [chunk][dk]; v [chunk][MM_COLS]; scalars [chunk][4]; gates [chunk][2]
   const int dk = g.dk, dv = g.dv;
-  const int per = 3 * dk + 8;
+  float* sq = sm;
+  float* sk = sq + chunk * dk;
+  float* sg = sk + chunk * dk;
+  float* sv = sg + (MODE == 1 ? chunk * dk : 0);
+  float* sc = sv + chunk * MM_COLS;
+  float* sgate = sc + chunk * 4;
   const int row = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * MM_COLS;
   const int qh = h / (g.H / g.QH);
   const int lane4 = threadIdx.x & (MM_LANES - 1);
-  const int j = j0 + (threadIdx.x >> 2);
+  const int col = threadIdx.x >> 2;
+  const int j = j0 + col;
   const bool col_ok = j < dv;
   pdl_wait();
   pdl_trigger();
@@ -117,87 +195,97 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(MatrixMemoryA
     if (MODE == 0 && i < dk) nn[r] = g.n_state[((int64_t)slot * g.H + h) * dk + i];
   }
   float m_run = MODE == 0 ? g.m_state[(int64_t)slot * g.H + h] : 0.0f;
-  mm_stage<MODE>(g, t0, h, qh, sm, sm + dk, sm + 2 * dk, sm + 3 * dk, m_run);
-  __syncthreads();
-  for (int t = t0; t < t1; ++t) {
-    const int b = (t - t0) & 1;
-    float* cur = sm + b * per;
-    float* nxt = sm + (b ^ 1) * per;
-    // the next token's vectors go to the other buffer while this token is worked on
-    if (t + 1 < t1) mm_stage<MODE>(g, t + 1, h, qh, nxt, nxt + dk, nxt + 2 * dk, nxt + 3 * dk, m_run);
-    const float* sq = cur;
-    const float* sk = cur + dk;
-    const float* sg = cur + 2 * dk;
-    const float* sc = cur + 3 * dk;
-    const float vj = col_ok ? mm_load(g.v, g.qkv_dtype, (int64_t)t * g.ldv + (int64_t)h * dv + j) : 0.0f;
-    float o;
-    if (MODE == 0) {
-      const float a = sc[0], bw = sc[1];
-      const float bv = bw * vj;
-      float num = 0.0f, nq = 0.0f;
+  for (int c0 = t0; c0 < t1; c0 += chunk) {
+    const int n = min(chunk, t1 - c0);
+    mm_stage_chunk<MODE>(g, c0, n, h, qh, j0, sq, sk, sg, sv, sc, sgate, m_run);
+    for (int tt = 0; tt < n; ++tt) {
+      const float* q_ = sq + tt * dk;
+      const float* k_ = sk + tt * dk;
+      const float vj = sv[tt * MM_COLS + col];
+      float o;
+      if (MODE == 0) {
+        const float a = sc[tt * 4], bw = sc[tt * 4 + 1];
+        const float bv = bw * vj;
+        float num = 0.0f, nq = 0.0f;
 #pragma unroll
-      for (int r = 0; r < NR; ++r) {
-        const int i = r * MM_LANES + lane4;
-        const float kk = i < dk ? sk[i] : 0.0f, qq = i < dk ? sq[i] : 0.0f;
-        S[r] = fmaf(a, S[r], kk * bv);
-        nn[r] = fmaf(a, nn[r], bw * kk);
-        num = fmaf(S[r], qq, num);
-        nq = fmaf(nn[r], qq, nq);
-      }
-      num += __shfl_xor_sync(0xffffffffu, num, 1);
-      nq += __shfl_xor_sync(0xffffffffu, nq, 1);
-      num += __shfl_xor_sync(0xffffffffu, num, 2);
-      nq += __shfl_xor_sync(0xffffffffu, nq, 2);
-      o = num / (fmaxf(fabsf(nq), sc[2]) + 1e-6f);
-    } else {
-      float dot = 0.0f;
+        for (int r = 0; r < NR; ++r) {
+          const int i = r * MM_LANES + lane4;
+          const float kk = i < dk ? k_[i] : 0.0f, qq = i < dk ? q_[i] : 0.0f;
+          S[r] = fmaf(a, S[r], kk * bv);
+          nn[r] = fmaf(a, nn[r], bw * kk);
+          num = fmaf(S[r], qq, num);
+          nq = fmaf(nn[r], qq, nq);
+        }
+        num += __shfl_xor_sync(0xffffffffu, num, 1);
+        nq += __shfl_xor_sync(0xffffffffu, nq, 1);
+        num += __shfl_xor_sync(0xffffffffu, num, 2);
+        nq += __shfl_xor_sync(0xffffffffu, nq, 2);
+        o = num / (fmaxf(fabsf(nq), sc[tt * 4 + 2]) + 1e-6f);
+      } else {
+        const float* g_ = sg + tt * dk;
+        float dot = 0.0f;
 #pragma unroll
-      for (int r = 0; r < NR; ++r) {
-        const int i = r * MM_LANES + lane4;
-        const float gg = i < dk ? sg[i] : 1.0f, kk = i < dk ? sk[i] : 0.0f;
-        S[r] *= gg;
-        dot = fmaf(S[r], kk, dot);
-      }
-      dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-      dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-      const float u = sc[3] * (vj - dot);
-      float num = 0.0f;
+        for (int r = 0; r < NR; ++r) {
+          const int i = r * MM_LANES + lane4;
+          const float gg = i < dk ? g_[i] : 1.0f, kk = i < dk ? k_[i] : 0.0f;
+          S[r] *= gg;
+          dot = fmaf(S[r], kk, dot);
+        }
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        const float u = sc[tt * 4 + 3] * (vj - dot);
+        float num = 0.0f;
 #pragma unroll
-      for (int r = 0; r < NR; ++r) {
-        const int i = r * MM_LANES + lane4;
-        const float kk = i < dk ? sk[i] : 0.0f, qq = i < dk ? sq[i] : 0.0f;
-        S[r] = fmaf(kk, u, S[r]);
-        num = fmaf(S[r], qq, num);
+        for (int r = 0; r < NR; ++r) {
+          const int i = r * MM_LANES + lane4;
+          const float kk = i < dk ? k_[i] : 0.0f, qq = i < dk ? q_[i] : 0.0f;
+          S[r] = fmaf(kk, u, S[r]);
+          num = fmaf(S[r], qq, num);
+        }
+        num += __shfl_xor_sync(0xffffffffu, num, 1);
+        num += __shfl_xor_sync(0xffffffffu, num, 2);
+        o = num;
       }
-      num += __shfl_xor_sync(0xffffffffu, num, 1);
-      num += __shfl_xor_sync(0xffffffffu, num, 2);
-      o = num;
+      if (col_ok && lane4 == 0) g.out[(int64_t)(c0 + tt) * g.H * dv + (int64_t)h * dv + j] = o;
     }
-    if (col_ok && lane4 == 0) g.out[(int64_t)t * g.H * dv + (int64_t)h * dv + j] = o;
-    __syncthreads();                                   // the next buffer is complete and this one is free
+    __syncthreads();                                   // the chunk's vectors are free for the next one
   }
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
     const int i = r * MM_LANES + lane4;
     if (col_ok && i < dk) Sp[(int64_t)i * dv + j] = S[r];
     // the normaliser and the maximum are the same in every block of a head: the first block's first column writes them
-    if (MODE == 0 && blockIdx.z == 0 && (threadIdx.x >> 2) == 0 && i < dk)
+    if (MODE == 0 && blockIdx.z == 0 && col == 0 && i < dk)
       g.n_state[((int64_t)slot * g.H + h) * dk + i] = nn[r];
   }
   if (MODE == 0 && blockIdx.z == 0 && threadIdx.x == 0) g.m_state[(int64_t)slot * g.H + h] = m_run;
 }
 
-template <int MODE>
-static int mm_launch(const MatrixMemoryArgs& g, int rows, cudaStream_t stream) {
-  const dim3 grid(rows, g.H, ceil_div(g.dv, MM_COLS));
-  const size_t smem = 2 * (size_t)(3 * g.dk + 8) * sizeof(float);
-  const int nr = ceil_div(g.dk, MM_LANES);
-  if (nr <= 8) launch_pdl(matrix_memory_kernel<MODE, 8>, grid, dim3(MM_THREADS), smem, stream, g);
-  else if (nr <= 16) launch_pdl(matrix_memory_kernel<MODE, 16>, grid, dim3(MM_THREADS), smem, stream, g);
-  else if (nr <= 32) launch_pdl(matrix_memory_kernel<MODE, 32>, grid, dim3(MM_THREADS), smem, stream, g);
-  else if (nr <= 64) launch_pdl(matrix_memory_kernel<MODE, 64>, grid, dim3(MM_THREADS), smem, stream, g);
-  else { set_error("matrix_memory: keys of %d features are too wide (at most 256)", g.dk); return ERR_UNSUPPORTED; }
+template <int MODE, int NR>
+static int mm_launch_nr(const MatrixMemoryArgs& g, dim3 grid, int chunk, size_t smem, cudaStream_t stream) {
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(matrix_memory_kernel<MODE, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) { set_error("matrix_memory: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e)); return (int)e; }
+  }
+  launch_pdl(matrix_memory_kernel<MODE, NR>, grid, dim3(MM_THREADS), smem, stream, g, chunk);
   return launch_status("matrix_memory");
+}
+
+template <int MODE>
+static int mm_launch(const MatrixMemoryArgs& g, int rows, int max_new, cudaStream_t stream) {
+  const dim3 grid(rows, g.H, ceil_div(g.dv, MM_COLS));
+  // tokens staged at once: as many as a row brings, up to MM_CHUNK (at most as many as the block has threads) and to
+  // what fits 96 KB of shared memory
+  const size_t per_token = (size_t)((MODE == 1 ? 3 : 2) * g.dk + MM_COLS + 6) * sizeof(float);
+  const int chunk = max(1, min(min(max_new, MM_CHUNK), (int)(96 * 1024 / per_token)));
+  const size_t smem = (size_t)chunk * per_token;
+  const int nr = ceil_div(g.dk, MM_LANES);
+  if (nr <= 8) return mm_launch_nr<MODE, 8>(g, grid, chunk, smem, stream);
+  if (nr <= 16) return mm_launch_nr<MODE, 16>(g, grid, chunk, smem, stream);
+  if (nr <= 32) return mm_launch_nr<MODE, 32>(g, grid, chunk, smem, stream);
+  if (nr <= 64) return mm_launch_nr<MODE, 64>(g, grid, chunk, smem, stream);
+  set_error("matrix_memory: keys of %d features are too wide (at most 256)", g.dk);
+  return ERR_UNSUPPORTED;
 }
 
 // ---------------------------------------------------------------------------------------------------------------------
@@ -212,7 +300,7 @@ struct ConvPrepArgs {
   float* state;                                      // [slots, channels, taps - 1], oldest first
   const int* slot_ids; const int* row_start;
   float* out;                                        // [T, channels]: q | k | v
-  int channels, chunks;
+  int channels, chunks, chunk_tokens;
 };
 
 __global__ void __launch_bounds__(CONV_WARPS * 32) conv_prep_kernel(ConvPrepArgs g) {
@@ -229,9 +317,9 @@ __global__ void __launch_bounds__(CONV_WARPS * 32) conv_prep_kernel(ConvPrepArgs
   const int c_out = (sec == 0 ? 0 : (sec == 1 ? g.heads[0] * g.dim[0] : g.heads[0] * g.dim[0] + g.heads[1] * g.dim[1])) + c_sec;
   const int row = blockIdx.x / g.chunks, chunk = blockIdx.x - row * g.chunks;
   const int t0 = __ldcg(g.row_start + row), t1 = __ldcg(g.row_start + row + 1);
-  const int first = t0 + chunk * CONV_CHUNK;
+  const int first = t0 + chunk * g.chunk_tokens;
   if (first >= t1) return;
-  const int last = min(t1, first + CONV_CHUNK);
+  const int last = min(t1, first + g.chunk_tokens);
   const int nt = g.n_taps;
   const int slot = __ldcg(g.slot_ids + row);
   const float* st = g.state + ((int64_t)slot * g.channels + c_out) * (nt - 1);
@@ -298,14 +386,16 @@ __global__ void __launch_bounds__(CONV_WARPS * 32) conv_prep_kernel(ConvPrepArgs
 using namespace exl3;
 
 static bool mm_dtype_ok(int d) { return d == DT_F32 || d == DT_BF16; }
+// whether groups of four elements from p on can be read at once (16 bytes of float32, 8 of bfloat16)
+static bool mm_aligned(const void* p, int dtype) { return (reinterpret_cast<uintptr_t>(p) & (dtype == DT_F32 ? 15u : 7u)) == 0; }
 
 extern "C" int exl3_mlstm_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
                                int qkv_dtype, const void* zi, const void* zf, int gate_dtype, int64_t ld_gate, float cap,
                                float q_scale, float* s_state, float* n_state, float* m_state, const int* slot_ids,
                                const int* row_start, float* out, int rows, int T, int heads, int dk, int dv,
-                               cudaStream_t stream) {
+                               int max_new, cudaStream_t stream) {
   if (T == 0 || rows == 0) return 0;
-  if (T < 0 || rows < 0 || heads < 1 || dk < 1 || dv < 1 || !(cap > 0.0f) || !mm_dtype_ok(qkv_dtype) || !mm_dtype_ok(gate_dtype) ||
+  if (T < 0 || rows < 0 || heads < 1 || dk < 1 || dv < 1 || max_new < 1 || !(cap > 0.0f) || !mm_dtype_ok(qkv_dtype) || !mm_dtype_ok(gate_dtype) ||
       heads > 65535 || dv > 65535 * MM_COLS) {
     set_error("mlstm_scan: bad sizes rows=%d T=%d heads=%d dk=%d dv=%d cap=%g", rows, T, heads, dk, dv, (double)cap);
     return ERR_BAD_ARGUMENT;
@@ -315,16 +405,17 @@ extern "C" int exl3_mlstm_scan(const void* q, int64_t ldq, const void* k, int64_
   g.zi = zi; g.zf = zf; g.gate_dtype = gate_dtype; g.ld_gate = ld_gate; g.cap = cap;
   g.s_state = s_state; g.n_state = n_state; g.m_state = m_state; g.slot_ids = slot_ids; g.row_start = row_start;
   g.out = out; g.H = heads; g.QH = heads; g.dk = dk; g.dv = dv;
-  return mm_launch<0>(g, rows, stream);
+  g.vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && mm_aligned(q, qkv_dtype) && mm_aligned(k, qkv_dtype);
+  return mm_launch<0>(g, rows, max_new, stream);
 }
 
 extern "C" int exl3_delta_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv,
                                int qkv_dtype, const void* zb, int zb_dtype, int64_t ld_zb, const void* za, int za_dtype,
                                int64_t ld_za, const float* a_log, const float* dt_bias, float* s_state,
                                const int* slot_ids, const int* row_start, float* out, int rows, int T, int heads,
-                               int qk_heads, int dk, int dv, cudaStream_t stream) {
+                               int qk_heads, int dk, int dv, int max_new, cudaStream_t stream) {
   if (T == 0 || rows == 0) return 0;
-  if (T < 0 || rows < 0 || heads < 1 || qk_heads < 1 || heads % qk_heads != 0 || dk < 1 || dv < 1 || !mm_dtype_ok(qkv_dtype) ||
+  if (T < 0 || rows < 0 || max_new < 1 || heads < 1 || qk_heads < 1 || heads % qk_heads != 0 || dk < 1 || dv < 1 || !mm_dtype_ok(qkv_dtype) ||
       !mm_dtype_ok(zb_dtype) || !mm_dtype_ok(za_dtype) || heads > 65535 || dv > 65535 * MM_COLS) {
     set_error("delta_scan: bad sizes rows=%d T=%d heads=%d on %d dk=%d dv=%d", rows, T, heads, qk_heads, dk, dv);
     return ERR_BAD_ARGUMENT;
@@ -334,7 +425,9 @@ extern "C" int exl3_delta_scan(const void* q, int64_t ldq, const void* k, int64_
   g.zb = zb; g.zb_dtype = zb_dtype; g.ld_zb = ld_zb; g.za = za; g.za_dtype = za_dtype; g.ld_za = ld_za;
   g.a_log = a_log; g.dt_bias = dt_bias; g.s_state = s_state; g.slot_ids = slot_ids; g.row_start = row_start;
   g.out = out; g.H = heads; g.QH = qk_heads; g.dk = dk; g.dv = dv;
-  return mm_launch<1>(g, rows, stream);
+  g.vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ld_za % 4 == 0 && mm_aligned(q, qkv_dtype) &&
+          mm_aligned(k, qkv_dtype) && mm_aligned(za, za_dtype);
+  return mm_launch<1>(g, rows, max_new, stream);
 }
 
 extern "C" int exl3_conv_prep_max_taps() { return CONV_MAX_TAPS; }
@@ -359,7 +452,10 @@ extern "C" int exl3_conv_prep(const void* x, int x_dtype, int64_t ldx, int q_off
   g.dim[0] = dk; g.dim[1] = dk; g.dim[2] = dv;
   g.n_taps = n_taps; g.eps = eps; g.q_scale = q_scale; g.state = state; g.slot_ids = slot_ids; g.row_start = row_start;
   g.out = out; g.channels = 2 * qk_heads * dk + v_heads * dv;
-  g.chunks = ceil_div(max_new, CONV_CHUNK);
+  // tokens a warp walks: few, so that many warps hide each other's loads, but at least as many as the taps reach back
+  // (then only a row's first chunk reads the kept inputs)
+  g.chunk_tokens = max(CONV_MIN_CHUNK, n_taps - 1);
+  g.chunks = ceil_div(max_new, g.chunk_tokens);
   const int units = 2 * qk_heads + v_heads;
   const int64_t bx = (int64_t)rows * g.chunks;
   if (bx > 0x7fffffffLL || ceil_div(units, CONV_WARPS) > 65535) { set_error("conv_prep: grid too large"); return ERR_UNSUPPORTED; }

@@ -908,24 +908,27 @@ def attn_prefill_tc(q: torch.Tensor, q_row_stride: int, out: torch.Tensor, k_poo
                     block_table: torch.Tensor, row_start: torch.Tensor, row_pos0: torch.Tensor,
                     tile_seq: torch.Tensor, tile_q0: torch.Tensor, n_tiles: int, heads: int, kv_heads: int,
                     head_dim: int, page: int, window: int, scale: float, variant: int = 0, chunk: int = 0,
-                    sink: bool = False) -> torch.Tensor:
+                    sink: bool = False, keep_first: int = 0, softcap: float = 0.0,
+                    sink_vals: Optional[torch.Tensor] = None) -> torch.Tensor:
     """Causal attention of whole prompts on tcgen05 tensor cores (tiles of 128 queries; see
     attention_prefill_tc.cu).  ``k_pool`` / ``v_pool``: one layer's ``[pages, kv_heads, 64, head_dim]``.
     ``variant``: 0 lets the kernel choose by the number of blocks between a tile a block, four blocks per SM (heads
     of 64) and two tiles a block (the list's first with its last, and so on: list the tiles with the most keys
-    to visit first); 1, 2 and 3 force one of them (the same numbers every way).  ``chunk`` and ``sink`` as in
-    ``attn_tokens_ex``."""
+    to visit first); 1, 2 and 3 force one of them (the same numbers every way).  ``chunk``, ``sink``, ``keep_first``,
+    ``softcap`` and ``sink_vals`` as in ``attn_tokens_ex``."""
+    if sink_vals is not None and (sink_vals.dtype != torch.float32 or sink_vals.numel() != heads or not sink):
+        raise KernelLibraryError("attn_prefill_tc: sink scores must be float32 [heads], with the sink on")
     if k_pool.dtype != q.dtype or v_pool.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelLibraryError("attn_prefill_tc: q, cache and out differ in element type")
     _contig(k_pool, "k_pool")
     _contig(v_pool, "v_pool")
     pool_rows = k_pool.shape[0] * k_pool.shape[1] * k_pool.shape[2]
-    _check(library().exl3_attn_prefill_tc(
+    _check(library().exl3_attn_prefill_tc_opt(
         _ptr(q), _c_int64(q_row_stride), _c_int(q.shape[0]), _ptr(out), _ptr(k_pool), _ptr(v_pool),
         _c_int64(pool_rows), _ptr(block_table), _c_int(block_table.stride(0)), _ptr(row_start), _ptr(row_pos0),
         _ptr(tile_seq), _ptr(tile_q0), _c_int(n_tiles), _c_int(heads), _c_int(kv_heads), _c_int(head_dim),
         _c_int(page), _c_int(window), _c_int(chunk), _c_int(1 if sink else 0), _c_float(scale), _c_int(variant),
-        _stream()), "attn_prefill_tc")
+        _c_int(keep_first), _c_float(softcap), _ptr(sink_vals), _stream()), "attn_prefill_tc")
     return out
 
 
@@ -1369,11 +1372,12 @@ def hyper_step(x: torch.Tensor, streams: int, y: Optional[torch.Tensor], mix: Op
 
 def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zi: torch.Tensor, zf: torch.Tensor, cap: float,
                q_scale: float, s_state: torch.Tensor, n_state: torch.Tensor, m_state: torch.Tensor,
-               slot_ids: torch.Tensor, row_start: torch.Tensor, rows: int, heads: int, dk: int, dv: int) -> torch.Tensor:
+               slot_ids: torch.Tensor, row_start: torch.Tensor, rows: int, heads: int, dk: int, dv: int,
+               max_new: int) -> torch.Tensor:
     """The matrix memory with exponential gates over a step's packed tokens (see matrix_memory.cu).  ``q``, ``k``
     ``[T, heads * dk]``, ``v [T, heads * dv]`` and the gates' pre-activations ``zi``, ``zf [T, heads]`` may be views
     with their own row pitch; states float32 ``[slots, heads, dk, dv]``, ``[slots, heads, dk]``, ``[slots, heads]``
-    are read and written at ``slot_ids``.  Returns float32 ``[T, heads * dv]``."""
+    are read and written at ``slot_ids``; ``max_new`` is the most tokens a row brings.  Returns float32 ``[T, heads * dv]``."""
     T = q.shape[0]
     for t, name in ((q, "q"), (k, "k"), (v, "v"), (zi, "zi"), (zf, "zf")):
         if t.stride(1) != 1:
@@ -1388,13 +1392,13 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zi: torch.Tens
         _ptr(q), _c_int64(q.stride(0)), _ptr(k), _c_int64(k.stride(0)), _ptr(v), _c_int64(v.stride(0)),
         _c_int(dtype_code(q.dtype)), _ptr(zi), _ptr(zf), _c_int(dtype_code(zi.dtype)), _c_int64(zi.stride(0)),
         _c_float(cap), _c_float(q_scale), _ptr(s_state), _ptr(n_state), _ptr(m_state), _ptr(slot_ids), _ptr(row_start),
-        _ptr(out), _c_int(rows), _c_int(T), _c_int(heads), _c_int(dk), _c_int(dv), _stream()), "mlstm_scan")
+        _ptr(out), _c_int(rows), _c_int(T), _c_int(heads), _c_int(dk), _c_int(dv), _c_int(max_new), _stream()), "mlstm_scan")
     return out
 
 
 def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zb: torch.Tensor, za: torch.Tensor,
                a_log: torch.Tensor, dt_bias: torch.Tensor, s_state: torch.Tensor, slot_ids: torch.Tensor,
-               row_start: torch.Tensor, rows: int, heads: int, qk_heads: int, dk: int, dv: int) -> torch.Tensor:
+               row_start: torch.Tensor, rows: int, heads: int, qk_heads: int, dk: int, dv: int, max_new: int) -> torch.Tensor:
     """The gated delta rule over a step's packed tokens (see matrix_memory.cu): ``q``, ``k [T, qk_heads * dk]``,
     ``v [T, heads * dv]`` (one element type), ``zb [T, heads]`` (beta before its sigmoid), ``za [T, heads * dk]``
     (the decay's pre-activation, before ``dt_bias``), ``a_log [heads]``, ``dt_bias [heads * dk]`` float32; state
@@ -1416,7 +1420,7 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zb: torch.Tens
         _c_int(dtype_code(q.dtype)), _ptr(zb), _c_int(dtype_code(zb.dtype)), _c_int64(zb.stride(0)), _ptr(za),
         _c_int(dtype_code(za.dtype)), _c_int64(za.stride(0)), _ptr(a_log), _ptr(dt_bias), _ptr(s_state), _ptr(slot_ids),
         _ptr(row_start), _ptr(out), _c_int(rows), _c_int(T), _c_int(heads), _c_int(qk_heads), _c_int(dk), _c_int(dv),
-        _stream()), "delta_scan")
+        _c_int(max_new), _stream()), "delta_scan")
     return out
 
 
@@ -1460,4 +1464,18 @@ def scaled_sum2(a: torch.Tensor, b: torch.Tensor, sa: float, sb: float) -> torch
     out = torch.empty(a.shape, dtype=torch.float32, device=a.device)
     _check(library().exl3_scaled_sum2(_ptr(a), _ptr(b), _c_int(dtype_code(a.dtype)), _c_float(sa), _c_float(sb), _ptr(out),
                                       _c_int64(a.numel()), _stream()), "scaled_sum2")
+    return out
+
+
+def gemm_few_out(x: torch.Tensor, w: torch.Tensor, bias: Optional[torch.Tensor]) -> torch.Tensor:
+    """``x @ w.T (+ bias)`` as float32 for a handful of output features and many rows (a warp a row; see gemm_simt.cu)."""
+    M, Kd = x.shape
+    N = w.shape[0]
+    if x.stride(1) != 1 or w.shape[1] != Kd or x.dtype != w.dtype or (bias is not None and bias.dtype != w.dtype):
+        raise KernelLibraryError("gemm_few_out: x, w and bias must share an element type and fit")
+    _contig(w, "w")
+    out = torch.empty((M, N), dtype=torch.float32, device=x.device)
+    _check(library().exl3_gemm_few_out(_ptr(x), _c_int64(x.stride(0)), _ptr(w), _ptr(bias), _ptr(out),
+                                       _c_int(dtype_code(x.dtype)), _c_int(M), _c_int(N), _c_int(Kd), _stream()),
+           "gemm_few_out")
     return out

