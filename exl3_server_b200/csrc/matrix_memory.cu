@@ -7,7 +7,7 @@
 //   i = cap tanh(zi / cap),  f = logsigmoid(cap tanh(zf / cap)),  m' = max(f + m, i)        (m starts at 0)
 //   S' = exp(f + m - m') S + exp(i - m') k v^T,   n' likewise with k alone
 //   o  = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)                                          (q times q_scale)
-// State: S, n [dk], m.
+// State: S (kept column by column, [dv][dk]), n [dk], m.
 //
 // Mode 1, the gated delta rule.  Per head, with a decay per key channel g = exp(-exp(A_h) softplus(za + dt_bias)) and
 // beta = sigmoid(zb):
@@ -15,8 +15,8 @@
 // Query and key heads may be shared by several value heads (head h reads q/k head h / (heads / qk_heads)).
 //
 // Both: a block owns some columns of S of one (row, head) and walks the row's tokens in order; a column lives in the
-// registers of four neighbouring lanes (rows i = 4 j + lane % 4), the two dot products of a token are summed inside
-// the four lanes; q, k, the decays, the block's values and the tokens' scalars are staged in shared memory a chunk of
+// registers of L = 4 or 8 neighbouring lanes (rows i = L r + lane % L), the two dot products of a token are summed
+// inside those lanes; q, k, the decays, the block's values and the tokens' scalars are staged in shared memory a chunk of
 // tokens at a time (the gates' exponentials of a chunk side by side, only the running maximum in order), so that a
 // token's step reads shared memory only and a chunk's load latency is paid once.
 //
@@ -30,10 +30,8 @@
 
 namespace exl3 {
 
-constexpr int MM_LANES = 4;             // lanes that share a column
-constexpr int MM_COLS = 32;             // columns a block owns
-constexpr int MM_THREADS = MM_LANES * MM_COLS;
-constexpr int MM_CHUNK = 128;           // tokens whose vectors are staged in shared memory at once (at most MM_THREADS)
+constexpr int MM_COLS = 32;             // columns a block owns; a column is shared by L = 4 or 8 lanes (a template parameter)
+constexpr int MM_CHUNK = 128;           // tokens whose vectors are staged in shared memory at once (at most a block's threads)
 constexpr int CONV_MAX_TAPS = 8;
 constexpr int CONV_MIN_CHUNK = 4;       // tokens a warp walks at least
 constexpr int CONV_WARPS = 4;
@@ -69,7 +67,7 @@ struct MatrixMemoryArgs {
   const void* zb; int zb_dtype; int64_t ld_zb;        // [T, H]
   const void* za; int za_dtype; int64_t ld_za;        // [T, H * dk]
   const float* a_log; const float* dt_bias;           // [H], [H * dk]
-  float* s_state;                     // [slots, H, dk, dv]
+  float* s_state;                     // [slots, H, dv, dk]: a column of S is contiguous
   const int* slot_ids; const int* row_start;
   float* out;                         // [T, H * dv]
   int H, QH, dk, dv;
@@ -88,11 +86,11 @@ __device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, 
     // rows of q, k (and the decays' pre-activations) in 16-byte pieces, four pieces of each in flight a thread
     const int per = dk / 4;                           // pieces of four features in a token's row
     const float ea = MODE == 1 ? expf(__ldg(g.a_log + h)) : 0.0f;
-    for (int e0 = threadIdx.x; e0 < n * per; e0 += MM_THREADS * 4) {
+    for (int e0 = threadIdx.x; e0 < n * per; e0 += blockDim.x * 4) {
       float vq[4][4], vk[4][4], va[4][4];
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int e = e0 + u * MM_THREADS;
+        const int e = e0 + u * blockDim.x;
         if (e < n * per) {
           const int tt = e / per, i = (e - tt * per) * 4;
           const int64_t t = t0 + tt;
@@ -103,7 +101,7 @@ __device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, 
       }
 #pragma unroll
       for (int u = 0; u < 4; ++u) {
-        const int e = e0 + u * MM_THREADS;
+        const int e = e0 + u * blockDim.x;
         if (e < n * per) {
           const int tt = e / per, i = (e - tt * per) * 4;
 #pragma unroll
@@ -116,7 +114,7 @@ __device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, 
       }
     }
   } else {
-    for (int e = threadIdx.x; e < n * dk; e += MM_THREADS) {
+    for (int e = threadIdx.x; e < n * dk; e += blockDim.x) {
       const int tt = e / dk, i = e - tt * dk;
       const int64_t t = t0 + tt;
       sq[e] = mm_load(g.q, g.qkv_dtype, t * g.ldq + (int64_t)qh * dk + i) * g.q_scale;
@@ -127,7 +125,7 @@ __device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, 
       }
     }
   }
-  for (int e = threadIdx.x; e < n * MM_COLS; e += MM_THREADS) {
+  for (int e = threadIdx.x; e < n * MM_COLS; e += blockDim.x) {
     const int tt = e / MM_COLS, c = e - tt * MM_COLS;
     sv[e] = (j0 + c < dv) ? mm_load(g.v, g.qkv_dtype, (int64_t)(t0 + tt) * g.ldv + (int64_t)h * dv + j0 + c) : 0.0f;
   }
@@ -163,9 +161,10 @@ __device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, 
   __syncthreads();
 }
 
-// NR: rows of a column that one lane holds (dk <= 4 NR).
-template <int MODE, int NR>
-__global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(MatrixMemoryArgs g, int chunk) {
+// L: lanes that share a column (4 or 8); NR: rows of a column that one lane holds (dk <= L NR).  The state lies in
+// memory column by column, [dv][dk], so that the lanes of a column read and write neighbouring addresses.
+template <int MODE, int L, int NR>
+__global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemoryArgs g, int chunk) {
   extern __shared__ float sm[];                      // q, k, (g) [chunk][dk]; v [chunk][MM_COLS]; scalars [chunk][4]; gates [chunk][2]
   const int dk = g.dk, dv = g.dv;
   float* sq = sm;
@@ -176,8 +175,8 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(MatrixMemoryA
   float* sgate = sc + chunk * 4;
   const int row = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * MM_COLS;
   const int qh = h / (g.H / g.QH);
-  const int lane4 = threadIdx.x & (MM_LANES - 1);
-  const int col = threadIdx.x >> 2;
+  const int lane4 = threadIdx.x & (L - 1);          // this lane's place among the lanes of its column
+  const int col = threadIdx.x / L;
   const int j = j0 + col;
   const bool col_ok = j < dv;
   pdl_wait();
@@ -189,8 +188,8 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(MatrixMemoryA
   float S[NR], nn[NR];
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
-    const int i = r * MM_LANES + lane4;
-    S[r] = (col_ok && i < dk) ? Sp[(int64_t)i * dv + j] : 0.0f;
+    const int i = r * L + lane4;
+    S[r] = (col_ok && i < dk) ? Sp[(int64_t)j * dk + i] : 0.0f;
     nn[r] = 0.0f;
     if (MODE == 0 && i < dk) nn[r] = g.n_state[((int64_t)slot * g.H + h) * dk + i];
   }
@@ -209,41 +208,42 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(MatrixMemoryA
         float num = 0.0f, nq = 0.0f;
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
-          const int i = r * MM_LANES + lane4;
+          const int i = r * L + lane4;
           const float kk = i < dk ? k_[i] : 0.0f, qq = i < dk ? q_[i] : 0.0f;
           S[r] = fmaf(a, S[r], kk * bv);
           nn[r] = fmaf(a, nn[r], bw * kk);
           num = fmaf(S[r], qq, num);
           nq = fmaf(nn[r], qq, nq);
         }
-        num += __shfl_xor_sync(0xffffffffu, num, 1);
-        nq += __shfl_xor_sync(0xffffffffu, nq, 1);
-        num += __shfl_xor_sync(0xffffffffu, num, 2);
-        nq += __shfl_xor_sync(0xffffffffu, nq, 2);
-        o = num / (fmaxf(fabsf(nq), sc[tt * 4 + 2]) + 1e-6f);
+#pragma unroll
+        for (int o2 = 1; o2 < L; o2 <<= 1) {
+          num += __shfl_xor_sync(0xffffffffu, num, o2);
+          nq += __shfl_xor_sync(0xffffffffu, nq, o2);
+        }
+        o = __fdividef(num, fmaxf(fabsf(nq), sc[tt * 4 + 2]) + 1e-6f);
       } else {
         const float* g_ = sg + tt * dk;
         float dot = 0.0f;
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
-          const int i = r * MM_LANES + lane4;
+          const int i = r * L + lane4;
           const float gg = i < dk ? g_[i] : 1.0f, kk = i < dk ? k_[i] : 0.0f;
           S[r] *= gg;
           dot = fmaf(S[r], kk, dot);
         }
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+#pragma unroll
+        for (int o2 = 1; o2 < L; o2 <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o2);
         const float u = sc[tt * 4 + 3] * (vj - dot);
         float num = 0.0f;
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
-          const int i = r * MM_LANES + lane4;
+          const int i = r * L + lane4;
           const float kk = i < dk ? k_[i] : 0.0f, qq = i < dk ? q_[i] : 0.0f;
           S[r] = fmaf(kk, u, S[r]);
           num = fmaf(S[r], qq, num);
         }
-        num += __shfl_xor_sync(0xffffffffu, num, 1);
-        num += __shfl_xor_sync(0xffffffffu, num, 2);
+#pragma unroll
+        for (int o2 = 1; o2 < L; o2 <<= 1) num += __shfl_xor_sync(0xffffffffu, num, o2);
         o = num;
       }
       if (col_ok && lane4 == 0) g.out[(int64_t)(c0 + tt) * g.H * dv + (int64_t)h * dv + j] = o;
@@ -252,8 +252,8 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(MatrixMemoryA
   }
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
-    const int i = r * MM_LANES + lane4;
-    if (col_ok && i < dk) Sp[(int64_t)i * dv + j] = S[r];
+    const int i = r * L + lane4;
+    if (col_ok && i < dk) Sp[(int64_t)j * dk + i] = S[r];
     // the normaliser and the maximum are the same in every block of a head: the first block's first column writes them
     if (MODE == 0 && blockIdx.z == 0 && col == 0 && i < dk)
       g.n_state[((int64_t)slot * g.H + h) * dk + i] = nn[r];
@@ -261,13 +261,13 @@ __global__ void __launch_bounds__(MM_THREADS) matrix_memory_kernel(MatrixMemoryA
   if (MODE == 0 && blockIdx.z == 0 && threadIdx.x == 0) g.m_state[(int64_t)slot * g.H + h] = m_run;
 }
 
-template <int MODE, int NR>
+template <int MODE, int L, int NR>
 static int mm_launch_nr(const MatrixMemoryArgs& g, dim3 grid, int chunk, size_t smem, cudaStream_t stream) {
   if (smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(matrix_memory_kernel<MODE, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(matrix_memory_kernel<MODE, L, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_error("matrix_memory: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e)); return (int)e; }
   }
-  launch_pdl(matrix_memory_kernel<MODE, NR>, grid, dim3(MM_THREADS), smem, stream, g, chunk);
+  launch_pdl(matrix_memory_kernel<MODE, L, NR>, grid, dim3(L * MM_COLS), smem, stream, g, chunk);
   return launch_status("matrix_memory");
 }
 
@@ -279,11 +279,16 @@ static int mm_launch(const MatrixMemoryArgs& g, int rows, int max_new, cudaStrea
   const size_t per_token = (size_t)((MODE == 1 ? 3 : 2) * g.dk + MM_COLS + 6) * sizeof(float);
   const int chunk = max(1, min(min(max_new, MM_CHUNK), (int)(96 * 1024 / per_token)));
   const size_t smem = (size_t)chunk * per_token;
-  const int nr = ceil_div(g.dk, MM_LANES);
-  if (nr <= 8) return mm_launch_nr<MODE, 8>(g, grid, chunk, smem, stream);
-  if (nr <= 16) return mm_launch_nr<MODE, 16>(g, grid, chunk, smem, stream);
-  if (nr <= 32) return mm_launch_nr<MODE, 32>(g, grid, chunk, smem, stream);
-  if (nr <= 64) return mm_launch_nr<MODE, 64>(g, grid, chunk, smem, stream);
+  // Eight lanes a column from keys of 32 features on: twice the warps of four lanes a column to hide each other's
+  // waits, half the rows a lane walks for every token.  (Sixteen lanes a column were measured and lose: what a token
+  // costs a warp beyond its rows, the sums across lanes, the division, the store, is then paid by twice the warps, and
+  // the kernel is bound by the instructions it issues.)
+  if (g.dk < 32) return mm_launch_nr<MODE, 4, 8>(g, grid, chunk, smem, stream);
+  const int nr = ceil_div(g.dk, 8);
+  if (nr <= 4) return mm_launch_nr<MODE, 8, 4>(g, grid, chunk, smem, stream);
+  if (nr <= 8) return mm_launch_nr<MODE, 8, 8>(g, grid, chunk, smem, stream);
+  if (nr <= 16) return mm_launch_nr<MODE, 8, 16>(g, grid, chunk, smem, stream);
+  if (nr <= 32) return mm_launch_nr<MODE, 8, 32>(g, grid, chunk, smem, stream);
   set_error("matrix_memory: keys of %d features are too wide (at most 256)", g.dk);
   return ERR_UNSUPPORTED;
 }

@@ -1376,7 +1376,7 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zi: torch.Tens
                max_new: int) -> torch.Tensor:
     """The matrix memory with exponential gates over a step's packed tokens (see matrix_memory.cu).  ``q``, ``k``
     ``[T, heads * dk]``, ``v [T, heads * dv]`` and the gates' pre-activations ``zi``, ``zf [T, heads]`` may be views
-    with their own row pitch; states float32 ``[slots, heads, dk, dv]``, ``[slots, heads, dk]``, ``[slots, heads]``
+    with their own row pitch; states float32 ``[slots, heads, dv, dk]`` (the matrix column by column), ``[slots, heads, dk]``, ``[slots, heads]``
     are read and written at ``slot_ids``; ``max_new`` is the most tokens a row brings.  Returns float32 ``[T, heads * dv]``."""
     T = q.shape[0]
     for t, name in ((q, "q"), (k, "k"), (v, "v"), (zi, "zi"), (zf, "zf")):
@@ -1384,7 +1384,7 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zi: torch.Tens
             raise KernelLibraryError(f"mlstm_scan: rows of {name} must be dense")
     if q.dtype != k.dtype or q.dtype != v.dtype or zi.dtype != zf.dtype or zi.stride(0) != zf.stride(0):
         raise KernelLibraryError("mlstm_scan: q, k, v (and zi, zf) must agree in element type and pitch")
-    for t, shape in ((s_state, (heads, dk, dv)), (n_state, (heads, dk)), (m_state, (heads,))):
+    for t, shape in ((s_state, (heads, dv, dk)), (n_state, (heads, dk)), (m_state, (heads,))):
         if t.dtype != torch.float32 or tuple(t.shape[1:]) != shape or not t.is_contiguous():
             raise KernelLibraryError(f"mlstm_scan: a state of shape {tuple(t.shape)} must be contiguous float32 [slots, {shape}]")
     out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
@@ -1402,7 +1402,8 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zb: torch.Tens
     """The gated delta rule over a step's packed tokens (see matrix_memory.cu): ``q``, ``k [T, qk_heads * dk]``,
     ``v [T, heads * dv]`` (one element type), ``zb [T, heads]`` (beta before its sigmoid), ``za [T, heads * dk]``
     (the decay's pre-activation, before ``dt_bias``), ``a_log [heads]``, ``dt_bias [heads * dk]`` float32; state
-    float32 ``[slots, heads, dk, dv]``.  Returns float32 ``[T, heads * dv]``."""
+    float32 ``[slots, heads, dv, dk]`` (the matrix column by column); ``max_new`` is the most tokens a row brings.
+    Returns float32 ``[T, heads * dv]``."""
     T = q.shape[0]
     for t, name in ((q, "q"), (k, "k"), (v, "v"), (zb, "zb"), (za, "za")):
         if t.stride(1) != 1:
@@ -1412,8 +1413,8 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zb: torch.Tens
     if a_log.dtype != torch.float32 or dt_bias.dtype != torch.float32 or a_log.numel() != heads or \
             dt_bias.numel() != heads * dk:
         raise KernelLibraryError("delta_scan: a_log and dt_bias must be float32 [heads] and [heads * dk]")
-    if s_state.dtype != torch.float32 or tuple(s_state.shape[1:]) != (heads, dk, dv) or not s_state.is_contiguous():
-        raise KernelLibraryError(f"delta_scan: state {tuple(s_state.shape)} must be float32 [slots, {heads}, {dk}, {dv}]")
+    if s_state.dtype != torch.float32 or tuple(s_state.shape[1:]) != (heads, dv, dk) or not s_state.is_contiguous():
+        raise KernelLibraryError(f"delta_scan: state {tuple(s_state.shape)} must be float32 [slots, {heads}, {dv}, {dk}]")
     out = torch.empty((T, heads * dv), dtype=torch.float32, device=q.device)
     _check(library().exl3_delta_scan(
         _ptr(q), _c_int64(q.stride(0)), _ptr(k), _c_int64(k.stride(0)), _ptr(v), _c_int64(v.stride(0)),

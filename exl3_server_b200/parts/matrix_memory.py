@@ -7,7 +7,7 @@ range: ``m' = max(f + m, i)``, ``S' = exp(f + m - m') S + exp(i - m') k v^T``, `
 ``o = S'^T q / (max(|n' . q|, exp(-m')) + 1e-6)``.  Each head's ``o`` is divided by its root mean square, the heads
 are concatenated, multiplied by a weight and by ``sigmoid(Wg r)``, and projected by ``Wo``.  Parameters: ``key_dim``,
 ``value_dim``, ``gate_cap``, ``norm_eps``.  Tensors: ``q``, ``k``, ``v``, ``g``, ``o``, ``norm``, ``i``, ``i.b``,
-``f``, ``f.b``.  State per sequence: ``S [heads, dk, dv]``, ``n [heads, dk]``, ``m [heads]``.
+``f``, ``f.b``.  State per sequence: ``S`` (kept column by column, ``[heads, dv, dk]``), ``n [heads, dk]``, ``m [heads]``.
 
 ``gated_delta``: the gated delta rule.  ``q = Wq r``, ``k = Wk r`` (``qk_heads x dk``), ``v = Wv r`` (``heads x dv``;
 value head h reads q/k head ``h // (heads / qk_heads)``); each passes a short causal convolution over time per channel
@@ -19,7 +19,7 @@ is divided by its root mean square, times a weight ``[dv]`` shared by the heads,
 ``Wo``.  Parameters: ``qk_heads``, ``key_dim``, ``value_dim``, ``taps``, ``norm_eps``, ``unit_eps``; the ranks of the two
 low-rank pairs are whatever the checkpoint has.  Tensors: ``q``, ``q.conv``, ``k``, ``k.conv``, ``v``, ``v.conv``,
 ``b``, ``A_log``, ``norm``, ``a1``, ``a2``, ``dt_bias``, ``g1``, ``g2``, ``o``.  State per sequence: every channel's last
-``taps - 1`` inputs of the convolution, and ``S [heads, dk, dv]``.
+``taps - 1`` inputs of the convolution, and ``S`` (kept column by column, ``[heads, dv, dk]``).
 
 Gates, decays with their exponentials and softplus, unit norms, the states and the per-head norms are float32; the
 projections are the model's type (float32 results where the projection's kernel has them for free).
@@ -80,7 +80,7 @@ class MLSTM:
         return None
 
     def state_request(self):
-        return (StateRequest((self.H, self.dk, self.dv), torch.float32), StateRequest((self.H, self.dk), torch.float32),
+        return (StateRequest((self.H, self.dv, self.dk), torch.float32), StateRequest((self.H, self.dk), torch.float32),
                 StateRequest((self.H,), torch.float32))
 
     def forward(self, x: torch.Tensor, batch, kv, state) -> torch.Tensor:
@@ -173,7 +173,7 @@ class GatedDelta:
     def state_request(self):
         channels = 2 * self.G * self.dk + self.H * self.dv
         return (StateRequest((channels, self.taps - 1), torch.float32),
-                StateRequest((self.H, self.dk, self.dv), torch.float32))
+                StateRequest((self.H, self.dv, self.dk), torch.float32))
 
     def forward(self, x: torch.Tensor, batch, kv, state) -> torch.Tensor:
         if self.proj is None:

@@ -156,7 +156,7 @@ def test_mlstm_scan(dt, H, dk, dv, cap, lens):
     q, k, v = proj[:, :H * dk], proj[:, H * dk:2 * H * dk], proj[:, 2 * H * dk + 8:]
     z = (3.0 * torch.randn(T, 2 * H, generator=g))
     S0, n0, m0 = torch.randn(9, H, dk, dv, generator=g), torch.randn(9, H, dk, generator=g), torch.rand(9, H, generator=g)
-    S, n, m = S0.clone().to(DEV), n0.clone().to(DEV), m0.clone().to(DEV)
+    S, n, m = S0.transpose(2, 3).contiguous().to(DEV), n0.clone().to(DEV), m0.clone().to(DEV)     # the kernel keeps S column by column
     pd, zd = proj.to(DEV), z.to(DEV)
     out = k_.mlstm_scan(pd[:, :H * dk], pd[:, H * dk:2 * H * dk], pd[:, 2 * H * dk + 8:], zd[:, :H], zd[:, H:], cap,
                         dk ** -0.5, S, n, m, slot_ids, row_start, len(lens), H, dk, dv, max(lens))
@@ -179,7 +179,7 @@ def test_mlstm_scan(dt, H, dk, dv, cap, lens):
             t += 1
     # a division by a normaliser near its floor multiplies rounding: compare where it is not tiny against the largest
     close(out.reshape(T, H, dv), want, torch.float32 if dt == torch.float32 else dt, "outputs")
-    close(S, Sa, torch.float32, "matrix states, also of the slots that no row has")
+    close(S.transpose(2, 3), Sa, torch.float32, "matrix states, also of the slots that no row has")
     close(n, na, torch.float32, "normalisers")
     close(m, ma, torch.float32, "maxima")
 
@@ -201,7 +201,7 @@ def test_delta_scan(dt, H, G, dk, dv, lens):
     za = torch.randn(T, H * dk + 5, generator=g).to(dt)
     a_log, dt_bias = torch.log(0.05 + 1.5 * torch.rand(H, generator=g)), 2.0 * torch.rand(H * dk, generator=g) - 2.0
     S0 = torch.randn(9, H, dk, dv, generator=g)
-    S = S0.clone().to(DEV)
+    S = S0.transpose(2, 3).contiguous().to(DEV)           # the kernel keeps S column by column
     qkv = torch.cat([q, k, v], dim=1).to(DEV)
     out = k_.delta_scan(qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], zb.to(DEV)[:, 2:2 + H],
                         za.to(DEV)[:, :H * dk], a_log.to(DEV), dt_bias.to(DEV), S, slot_ids, row_start, len(lens), H, G, dk, dv, max(lens))
@@ -222,7 +222,7 @@ def test_delta_scan(dt, H, G, dk, dv, lens):
                 want[t, hd] = Sa[slot, hd].T @ qd[t, gq]
             t += 1
     close(out.reshape(T, H, dv), want, torch.float32, "outputs")
-    close(S, Sa, torch.float32, "states, also of the slots that no row has")
+    close(S.transpose(2, 3), Sa, torch.float32, "states, also of the slots that no row has")
 
 
 @pytest.mark.parametrize("dt", TYPES)
