@@ -367,7 +367,10 @@ int exl3_hyper_step(const float* xin, int s_in, float* xout, int S, const void* 
 int exl3_mlstm_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, int qkv_dtype,
                     const void* zi, const void* zf, int gate_dtype, int64_t ld_gate, float cap, float q_scale,
                     float* s_state, float* n_state, float* m_state, const int* slot_ids, const int* row_start,
-                    float* out, int rows, int T, int heads, int dk, int dv, int max_new, cudaStream_t stream);
+                    float* out, int rows, int T, int heads, int dk, int dv, int max_new, float* scratch,
+                    size_t scratch_bytes, cudaStream_t stream);
+// Bytes of scratch that exl3_mlstm_scan needs for a step (0 for steps of short rows).
+size_t exl3_mlstm_scan_scratch_bytes(int rows, int T, int heads, int dk, int dv, int max_new);
 int exl3_delta_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, int qkv_dtype,
                     const void* zb, int zb_dtype, int64_t ld_zb, const void* za, int za_dtype, int64_t ld_za,
                     const float* a_log, const float* dt_bias, float* s_state, const int* slot_ids, const int* row_start,

@@ -20,6 +20,15 @@
 // tokens at a time (the gates' exponentials of a chunk side by side, only the running maximum in order), so that a
 // token's step reads shared memory only and a chunk's load latency is paid once.
 //
+// Mode 0 for prompts: between two tokens the state only decays by one number a head (a = exp(f + m - m')) once the
+// running maxima are known, so a row is cut into pieces that run side by side.  A first kernel walks the gates of a row
+// in order and leaves a, b = exp(i - m') and exp(-m') per token; a second walks every piece but a row's last from a
+// zero state and leaves S and n at its end with the piece's whole decay (and keeps a copy of the states the step found);
+// a third folds, per element, a row's summaries in order into the states after every piece; a fourth starts every piece
+// from the state after the piece before it (a row's first from the copy) and walks it with the outputs; a row's last
+// piece writes the states back.  The pieces' borders count from the row's first token
+// of the step, so a prompt cut otherwise sums in another order: roundings differ, nothing else.
+//
 // conv_prep: per channel a causal convolution over time of `taps` taps (the last tap is the current token's), no bias,
 // zeros before the sequence's start, then SiLU; the q and k heads are then made unit vectors, x / sqrt(sum x^2 + eps),
 // and q is multiplied by q_scale.  The last taps - 1 inputs of every channel are per-sequence state.
@@ -72,6 +81,12 @@ struct MatrixMemoryArgs {
   float* out;                         // [T, H * dv]
   int H, QH, dk, dv;
   int vec;                            // q, k (and za) can be read four elements at a time
+  // Mode 0 for rows of many tokens: pieces of piece_len tokens side by side (see below).  pre [T, H, 4] holds every
+  // token's a, b, exp(-m'); phase 1 leaves a piece's summary, phase 2 folds the summaries before a piece into its start.
+  const float* pre;
+  int phase, piece_len, pieces;       // phase 0: a row is one piece and the gates are worked out here
+  float* sums;                        // [rows * pieces, H, dv * dk + dk + 1]: S and n at a piece's end from zero, its decay
+  float* init;                        // [rows, H, dv * dk + dk]: the states as the step found them
 };
 
 // Stages a chunk of up to MM_CHUNK tokens from t0 on into shared memory: q (scaled) and k as [token][dk], for mode 1 the
@@ -135,6 +150,16 @@ __device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, 
     __syncthreads();
     return;
   }
+  if (g.pre != nullptr) {                           // the tokens' factors were worked out by mlstm_gates_kernel
+    if (threadIdx.x < n) {
+      const float4 f4 = __ldcg(reinterpret_cast<const float4*>(g.pre) + (int64_t)(t0 + threadIdx.x) * g.H + h);
+      sc[threadIdx.x * 4 + 0] = f4.x;
+      sc[threadIdx.x * 4 + 1] = f4.y;
+      sc[threadIdx.x * 4 + 2] = f4.z;
+    }
+    __syncthreads();
+    return;
+  }
   // mode 0: the gates of the chunk's tokens side by side, then the running maximum in order, then the three factors
   if (threadIdx.x < n) {
     const int64_t t = t0 + threadIdx.x;
@@ -173,7 +198,9 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
   float* sv = sg + (MODE == 1 ? chunk * dk : 0);
   float* sc = sv + chunk * MM_COLS;
   float* sgate = sc + chunk * 4;
-  const int row = blockIdx.x, h = blockIdx.y, j0 = blockIdx.z * MM_COLS;
+  const int phase = MODE == 0 ? g.phase : 0;
+  const int row = phase ? blockIdx.x / g.pieces : blockIdx.x, piece = phase ? blockIdx.x - row * g.pieces : 0;
+  const int h = blockIdx.y, j0 = blockIdx.z * MM_COLS;
   const int qh = h / (g.H / g.QH);
   const int lane4 = threadIdx.x & (L - 1);          // this lane's place among the lanes of its column
   const int col = threadIdx.x / L;
@@ -181,19 +208,50 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
   const bool col_ok = j < dv;
   pdl_wait();
   pdl_trigger();
-  const int t0 = __ldcg(g.row_start + row), t1 = __ldcg(g.row_start + row + 1);
+  int t0 = __ldcg(g.row_start + row), t1 = __ldcg(g.row_start + row + 1);
   if (t0 >= t1) return;
   const int slot = __ldcg(g.slot_ids + row);
   float* Sp = g.s_state + ((int64_t)slot * g.H + h) * dk * dv;
   float S[NR], nn[NR];
+  const int row_end = t1;
+  const int rec = dv * dk + dk + 1;                  // floats of a piece's summary
+  float* init = phase ? g.init + ((int64_t)row * g.H + h) * (dv * dk + dk) : nullptr;
+  if (phase) {                                       // this block's piece of the row
+    t0 += piece * g.piece_len;
+    if (t0 >= t1) return;
+    t1 = min(t1, t0 + g.piece_len);
+  }
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
     const int i = r * L + lane4;
-    S[r] = (col_ok && i < dk) ? Sp[(int64_t)j * dk + i] : 0.0f;
+    S[r] = 0.0f;
     nn[r] = 0.0f;
-    if (MODE == 0 && i < dk) nn[r] = g.n_state[((int64_t)slot * g.H + h) * dk + i];
+    if (phase == 2) {
+      // the states at this piece's start: the step's own for a row's first piece, else what the fold left in the
+      // summary of the piece before
+      const float* from = piece == 0 ? init : g.sums + (((int64_t)row * g.pieces + piece - 1) * g.H + h) * rec;
+      if (col_ok && i < dk) S[r] = __ldcg(from + (int64_t)j * dk + i);
+      if (i < dk) nn[r] = __ldcg(from + dv * dk + i);
+    } else if (phase == 0 || piece == 0) {
+      if (col_ok && i < dk) S[r] = Sp[(int64_t)j * dk + i];
+      if (MODE == 0 && i < dk) nn[r] = g.n_state[((int64_t)slot * g.H + h) * dk + i];
+    }
   }
-  float m_run = MODE == 0 ? g.m_state[(int64_t)slot * g.H + h] : 0.0f;
+  if (phase == 1) {
+    if (piece == 0) {                                // the states as the step found them, for the third kernel
+#pragma unroll
+      for (int r = 0; r < NR; ++r) {
+        const int i = r * L + lane4;
+        if (col_ok && i < dk) init[(int64_t)j * dk + i] = S[r];
+        if (blockIdx.z == 0 && col == 0 && i < dk) init[dv * dk + i] = nn[r];
+        S[r] = 0.0f;                                 // a summary starts from nothing
+        nn[r] = 0.0f;
+      }
+    }
+    if (t1 >= row_end) return;                       // nobody needs the summary of a row's last piece
+  }
+  float decay = 1.0f;                                // the piece's whole decay (phase 1)
+  float m_run = (MODE == 0 && phase == 0) ? g.m_state[(int64_t)slot * g.H + h] : 0.0f;
   for (int c0 = t0; c0 < t1; c0 += chunk) {
     const int n = min(chunk, t1 - c0);
     mm_stage_chunk<MODE>(g, c0, n, h, qh, j0, sq, sk, sg, sv, sc, sgate, m_run);
@@ -205,6 +263,7 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
       if (MODE == 0) {
         const float a = sc[tt * 4], bw = sc[tt * 4 + 1];
         const float bv = bw * vj;
+        decay *= a;
         float num = 0.0f, nq = 0.0f;
 #pragma unroll
         for (int r = 0; r < NR; ++r) {
@@ -246,10 +305,22 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
         for (int o2 = 1; o2 < L; o2 <<= 1) num += __shfl_xor_sync(0xffffffffu, num, o2);
         o = num;
       }
-      if (col_ok && lane4 == 0) g.out[(int64_t)(c0 + tt) * g.H * dv + (int64_t)h * dv + j] = o;
+      if (col_ok && lane4 == 0 && phase != 1) g.out[(int64_t)(c0 + tt) * g.H * dv + (int64_t)h * dv + j] = o;
     }
     __syncthreads();                                   // the chunk's vectors are free for the next one
   }
+  if (phase == 1) {                                  // the piece's summary
+    float* sm_c = g.sums + (((int64_t)row * g.pieces + piece) * g.H + h) * rec;
+#pragma unroll
+    for (int r = 0; r < NR; ++r) {
+      const int i = r * L + lane4;
+      if (col_ok && i < dk) sm_c[(int64_t)j * dk + i] = S[r];
+      if (blockIdx.z == 0 && col == 0 && i < dk) sm_c[dv * dk + i] = nn[r];
+    }
+    if (blockIdx.z == 0 && threadIdx.x == 0) sm_c[dv * dk + dk] = decay;
+    return;
+  }
+  if (phase == 2 && t1 < row_end) return;            // only a row's last piece holds the row's last state
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
     const int i = r * L + lane4;
@@ -258,7 +329,77 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
     if (MODE == 0 && blockIdx.z == 0 && col == 0 && i < dk)
       g.n_state[((int64_t)slot * g.H + h) * dk + i] = nn[r];
   }
-  if (MODE == 0 && blockIdx.z == 0 && threadIdx.x == 0) g.m_state[(int64_t)slot * g.H + h] = m_run;
+  if (MODE == 0 && phase == 0 && blockIdx.z == 0 && threadIdx.x == 0) g.m_state[(int64_t)slot * g.H + h] = m_run;
+}
+
+// The gates of a row's tokens in order: per (row, head) a block that takes 128 tokens at a time (their caps, logsigmoid
+// and exponentials side by side, the running maximum in order) and leaves a, b, exp(-m') per token; the head's maximum
+// after the row goes back to the state.
+__global__ void __launch_bounds__(128) mlstm_gates_kernel(MatrixMemoryArgs g, float* __restrict__ pre) {
+  __shared__ float sgate[256];
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x, h = blockIdx.y;
+  const int t0 = __ldcg(g.row_start + row), t1 = __ldcg(g.row_start + row + 1);
+  if (t0 >= t1) return;
+  const int slot = __ldcg(g.slot_ids + row);
+  float m = g.m_state[(int64_t)slot * g.H + h];
+  for (int p0 = t0; p0 < t1; p0 += 128) {
+    const int n = min(128, t1 - p0);
+    if (threadIdx.x < n) {
+      const int64_t t = p0 + threadIdx.x;
+      const float zi = mm_load(g.zi, g.gate_dtype, t * g.ld_gate + h), zf = mm_load(g.zf, g.gate_dtype, t * g.ld_gate + h);
+      sgate[2 * threadIdx.x] = g.cap * tanhf(zi / g.cap);
+      sgate[2 * threadIdx.x + 1] = mm_logsigmoid(g.cap * tanhf(zf / g.cap));
+    }
+    __syncthreads();
+    float m_before = m, m_after = m;
+    for (int tt = 0; tt < n; ++tt) {
+      const float mn = fmaxf(sgate[2 * tt + 1] + m, sgate[2 * tt]);
+      if (tt == (int)threadIdx.x) { m_before = m; m_after = mn; }
+      m = mn;
+    }
+    if (threadIdx.x < n) {
+      const float gi = sgate[2 * threadIdx.x], gf = sgate[2 * threadIdx.x + 1];
+      reinterpret_cast<float4*>(pre)[(int64_t)(p0 + threadIdx.x) * g.H + h] =
+          make_float4(expf(gf + m_before - m_after), expf(gi - m_after), expf(-m_after), 0.0f);
+    }
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) g.m_state[(int64_t)slot * g.H + h] = m;
+}
+
+// Between the two walks: per element of S and n, through a row's pieces in order, s <- A s + (the piece's end from
+// zero), left in the piece's summary: the state after that piece, which is the next piece's start.
+__global__ void __launch_bounds__(256) mlstm_fold_kernel(MatrixMemoryArgs g) {
+  pdl_wait();
+  pdl_trigger();
+  const int row = blockIdx.x, h = blockIdx.y;
+  const int width = g.dv * g.dk + g.dk, rec = width + 1;
+  const int e = blockIdx.z * 256 + threadIdx.x;
+  const int n = __ldcg(g.row_start + row + 1) - __ldcg(g.row_start + row);
+  const int summaries = (n + g.piece_len - 1) / g.piece_len - 1;        // every piece of the row but its last has one
+  if (e >= width || summaries < 1) return;
+  float s = __ldcg(g.init + ((int64_t)row * g.H + h) * width + e);
+  float* base = g.sums + ((int64_t)row * g.pieces * g.H + h) * rec;
+  const int64_t step = (int64_t)g.H * rec;
+  for (int c0 = 0; c0 < summaries; c0 += 4) {
+    float A[4], v[4];
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (c0 + u < summaries) {
+        A[u] = __ldcg(base + (c0 + u) * step + width);
+        v[u] = __ldcg(base + (c0 + u) * step + e);
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      if (c0 + u < summaries) {
+        s = fmaf(A[u], s, v[u]);
+        base[(c0 + u) * step + e] = s;
+      }
+    }
+  }
 }
 
 template <int MODE, int L, int NR>
@@ -273,7 +414,8 @@ static int mm_launch_nr(const MatrixMemoryArgs& g, dim3 grid, int chunk, size_t 
 
 template <int MODE>
 static int mm_launch(const MatrixMemoryArgs& g, int rows, int max_new, cudaStream_t stream) {
-  const dim3 grid(rows, g.H, ceil_div(g.dv, MM_COLS));
+  const dim3 grid(g.phase ? rows * g.pieces : rows, g.H, ceil_div(g.dv, MM_COLS));
+  if (g.phase) max_new = g.piece_len;
   // tokens staged at once: as many as a row brings, up to MM_CHUNK (at most as many as the block has threads) and to
   // what fits 96 KB of shared memory
   const size_t per_token = (size_t)((MODE == 1 ? 3 : 2) * g.dk + MM_COLS + 6) * sizeof(float);
@@ -284,6 +426,12 @@ static int mm_launch(const MatrixMemoryArgs& g, int rows, int max_new, cudaStrea
   // costs a warp beyond its rows, the sums across lanes, the division, the store, is then paid by twice the warps, and
   // the kernel is bound by the instructions it issues.)
   if (g.dk < 32) return mm_launch_nr<MODE, 4, 8>(g, grid, chunk, smem, stream);
+  if (g.phase && g.dk <= 128) {
+    // pieces side by side fill the SMs with blocks: four lanes a column then cost the fewest instructions a column
+    const int nr4 = ceil_div(g.dk, 4);
+    if (nr4 <= 16) return mm_launch_nr<MODE, 4, 16>(g, grid, chunk, smem, stream);
+    return mm_launch_nr<MODE, 4, 32>(g, grid, chunk, smem, stream);
+  }
   const int nr = ceil_div(g.dk, 8);
   if (nr <= 4) return mm_launch_nr<MODE, 8, 4>(g, grid, chunk, smem, stream);
   if (nr <= 8) return mm_launch_nr<MODE, 8, 8>(g, grid, chunk, smem, stream);
@@ -391,6 +539,23 @@ __global__ void __launch_bounds__(CONV_WARPS * 32) conv_prep_kernel(ConvPrepArgs
 using namespace exl3;
 
 static bool mm_dtype_ok(int d) { return d == DT_F32 || d == DT_BF16; }
+
+// Rows of at least MLSTM_MIN_PIECED tokens run as pieces side by side: pieces of a multiple of 64 tokens, about 64 of
+// them over the step's rows.  Returns the bytes of scratch that takes (0: the rows run whole, in order).
+constexpr int MLSTM_MIN_PIECED = 256;
+static size_t mlstm_pieces(int rows, int T, int heads, int dk, int dv, int max_new, int* piece_len, int* pieces) {
+  if (max_new < MLSTM_MIN_PIECED) return 0;
+  const int len = 64 * exl3::ceil_div(exl3::ceil_div(T, 64), 64);       // about 64 pieces in all, whole sixty-fours
+  *piece_len = len < 64 ? 64 : len;
+  *pieces = exl3::ceil_div(max_new, *piece_len);
+  const size_t rec = (size_t)dv * dk + dk + 1;
+  return ((size_t)T * heads * 4 + (size_t)rows * heads * ((size_t)dv * dk + dk) + (size_t)rows * *pieces * heads * rec) * sizeof(float);
+}
+
+extern "C" size_t exl3_mlstm_scan_scratch_bytes(int rows, int T, int heads, int dk, int dv, int max_new) {
+  int a = 0, b = 0;
+  return mlstm_pieces(rows, T, heads, dk, dv, max_new, &a, &b);
+}
 // whether groups of four elements from p on can be read at once (16 bytes of float32, 8 of bfloat16)
 static bool mm_aligned(const void* p, int dtype) { return (reinterpret_cast<uintptr_t>(p) & (dtype == DT_F32 ? 15u : 7u)) == 0; }
 
@@ -398,7 +563,7 @@ extern "C" int exl3_mlstm_scan(const void* q, int64_t ldq, const void* k, int64_
                                int qkv_dtype, const void* zi, const void* zf, int gate_dtype, int64_t ld_gate, float cap,
                                float q_scale, float* s_state, float* n_state, float* m_state, const int* slot_ids,
                                const int* row_start, float* out, int rows, int T, int heads, int dk, int dv,
-                               int max_new, cudaStream_t stream) {
+                               int max_new, float* scratch, size_t scratch_bytes, cudaStream_t stream) {
   if (T == 0 || rows == 0) return 0;
   if (T < 0 || rows < 0 || heads < 1 || dk < 1 || dv < 1 || max_new < 1 || !(cap > 0.0f) || !mm_dtype_ok(qkv_dtype) || !mm_dtype_ok(gate_dtype) ||
       heads > 65535 || dv > 65535 * MM_COLS) {
@@ -411,6 +576,29 @@ extern "C" int exl3_mlstm_scan(const void* q, int64_t ldq, const void* k, int64_
   g.s_state = s_state; g.n_state = n_state; g.m_state = m_state; g.slot_ids = slot_ids; g.row_start = row_start;
   g.out = out; g.H = heads; g.QH = heads; g.dk = dk; g.dv = dv;
   g.vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && mm_aligned(q, qkv_dtype) && mm_aligned(k, qkv_dtype);
+  int piece_len = 0, pieces = 0;
+  const size_t need = mlstm_pieces(rows, T, heads, dk, dv, max_new, &piece_len, &pieces);
+  if (need == 0) return mm_launch<0>(g, rows, max_new, stream);
+  if (scratch == nullptr || scratch_bytes < need || !aligned16(scratch)) {
+    set_error("mlstm_scan: rows of up to %d tokens need %zu bytes of 16-byte aligned scratch, got %zu", max_new, need, scratch_bytes);
+    return ERR_SCRATCH;
+  }
+  float* pre = scratch;
+  g.pre = pre;
+  g.init = pre + (size_t)T * heads * 4;
+  g.sums = g.init + (size_t)rows * heads * ((size_t)dv * dk + dk);
+  g.piece_len = piece_len;
+  g.pieces = pieces;
+  launch_pdl(mlstm_gates_kernel, dim3(rows, heads), dim3(128), 0, stream, g, pre);
+  int rc = launch_status("mlstm_gates");
+  if (rc) return rc;
+  g.phase = 1;
+  rc = mm_launch<0>(g, rows, max_new, stream);
+  if (rc) return rc;
+  launch_pdl(mlstm_fold_kernel, dim3(rows, heads, ceil_div(dv * dk + dk, 256)), dim3(256), 0, stream, g);
+  rc = launch_status("mlstm_fold");
+  if (rc) return rc;
+  g.phase = 2;
   return mm_launch<0>(g, rows, max_new, stream);
 }
 

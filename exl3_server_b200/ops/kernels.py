@@ -1370,14 +1370,24 @@ def hyper_step(x: torch.Tensor, streams: int, y: Optional[torch.Tensor], mix: Op
     return xout, r
 
 
+def mlstm_scan_scratch_bytes(rows: int, T: int, heads: int, dk: int, dv: int, max_new: int) -> int:
+    """Bytes of float32 scratch that ``mlstm_scan`` needs for a step (0 for steps of short rows, which run in order)."""
+    lib = library()
+    lib.exl3_mlstm_scan_scratch_bytes.restype = _c_size_t
+    return int(lib.exl3_mlstm_scan_scratch_bytes(_c_int(rows), _c_int(T), _c_int(heads), _c_int(dk), _c_int(dv),
+                                                 _c_int(max_new)))
+
+
 def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zi: torch.Tensor, zf: torch.Tensor, cap: float,
                q_scale: float, s_state: torch.Tensor, n_state: torch.Tensor, m_state: torch.Tensor,
                slot_ids: torch.Tensor, row_start: torch.Tensor, rows: int, heads: int, dk: int, dv: int,
-               max_new: int) -> torch.Tensor:
+               max_new: int, scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The matrix memory with exponential gates over a step's packed tokens (see matrix_memory.cu).  ``q``, ``k``
     ``[T, heads * dk]``, ``v [T, heads * dv]`` and the gates' pre-activations ``zi``, ``zf [T, heads]`` may be views
     with their own row pitch; states float32 ``[slots, heads, dv, dk]`` (the matrix column by column), ``[slots, heads, dk]``, ``[slots, heads]``
-    are read and written at ``slot_ids``; ``max_new`` is the most tokens a row brings.  Returns float32 ``[T, heads * dv]``."""
+    are read and written at ``slot_ids``; ``max_new`` is the most tokens a row brings; ``scratch``: float32 memory of
+    ``mlstm_scan_scratch_bytes`` bytes when that is not 0 (rows of many tokens run as pieces side by side).  Returns float32
+    ``[T, heads * dv]``."""
     T = q.shape[0]
     for t, name in ((q, "q"), (k, "k"), (v, "v"), (zi, "zi"), (zf, "zf")):
         if t.stride(1) != 1:
@@ -1392,7 +1402,8 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zi: torch.Tens
         _ptr(q), _c_int64(q.stride(0)), _ptr(k), _c_int64(k.stride(0)), _ptr(v), _c_int64(v.stride(0)),
         _c_int(dtype_code(q.dtype)), _ptr(zi), _ptr(zf), _c_int(dtype_code(zi.dtype)), _c_int64(zi.stride(0)),
         _c_float(cap), _c_float(q_scale), _ptr(s_state), _ptr(n_state), _ptr(m_state), _ptr(slot_ids), _ptr(row_start),
-        _ptr(out), _c_int(rows), _c_int(T), _c_int(heads), _c_int(dk), _c_int(dv), _c_int(max_new), _stream()), "mlstm_scan")
+        _ptr(out), _c_int(rows), _c_int(T), _c_int(heads), _c_int(dk), _c_int(dv), _c_int(max_new), _ptr(scratch),
+        _c_size_t(0 if scratch is None else scratch.numel() * scratch.element_size()), _stream()), "mlstm_scan")
     return out
 
 

@@ -102,8 +102,10 @@ class MLSTM:
         q, k = proj[:, :H * dk], proj[:, H * dk:2 * H * dk]
         v = proj[:, 2 * H * dk:2 * H * dk + H * dv]
         g = proj[:, 2 * H * dk + H * dv:]
+        need = K.mlstm_scan_scratch_bytes(batch.n_rows, T, H, dk, dv, batch.max_new)
         o = K.mlstm_scan(q, k, v, z[:, :H], z[:, H:], self.cap, float(dk) ** -0.5, S, n, m, batch.slot_ids,
-                         batch.row_start, batch.n_rows, H, dk, dv, batch.max_new)
+                         batch.row_start, batch.n_rows, H, dk, dv, batch.max_new,
+                         scratch=batch.workspace.plain(need // 4) if need else None)
         y = K.head_norm_gate(o, self.norm_w, g, self.eps, H, dv, self.ctx.dtype, gate_kind="sigmoid")
         return self.o(y, out_dtype=self.o.wide_dtype(T))
 

@@ -145,8 +145,10 @@ def test_attention_with_a_window_that_keeps_the_first_keys(dt, H, G, d, dv, wind
 @pytest.mark.parametrize("dt", TYPES)
 @pytest.mark.parametrize("H, dk, dv, cap", [(3, 16, 24, 8.0), (1, 8, 40, 20.0), (2, 12, 20, 3.0), (2, 128, 64, 12.0),
                                             (2, 64, 130, 15.0), (1, 200, 8, 5.0)])
-@pytest.mark.parametrize("lens", [[5, 1, 9], [150, 3, 64]])
+@pytest.mark.parametrize("lens", [[5, 1, 9], [150, 3, 64], [600, 2, 257]])
 def test_mlstm_scan(dt, H, dk, dv, cap, lens):
+    """Rows of few tokens walk in order; with a row of 256 tokens or more the step runs as pieces of 64 tokens side by
+    side (the long rows in ten and five pieces, the short one in one)."""
     g = torch.Generator().manual_seed(6)
     k_ = K()
     slots = [4, 0, 6][:len(lens)]
@@ -158,8 +160,11 @@ def test_mlstm_scan(dt, H, dk, dv, cap, lens):
     S0, n0, m0 = torch.randn(9, H, dk, dv, generator=g), torch.randn(9, H, dk, generator=g), torch.rand(9, H, generator=g)
     S, n, m = S0.transpose(2, 3).contiguous().to(DEV), n0.clone().to(DEV), m0.clone().to(DEV)     # the kernel keeps S column by column
     pd, zd = proj.to(DEV), z.to(DEV)
+    need = k_.mlstm_scan_scratch_bytes(len(lens), T, H, dk, dv, max(lens))
+    assert (need > 0) == (max(lens) >= 256)
+    scratch = torch.full((need // 4 + 4,), float("nan"), device=DEV)[:need // 4] if need else None
     out = k_.mlstm_scan(pd[:, :H * dk], pd[:, H * dk:2 * H * dk], pd[:, 2 * H * dk + 8:], zd[:, :H], zd[:, H:], cap,
-                        dk ** -0.5, S, n, m, slot_ids, row_start, len(lens), H, dk, dv, max(lens))
+                        dk ** -0.5, S, n, m, slot_ids, row_start, len(lens), H, dk, dv, max(lens), scratch=scratch)
     want = torch.zeros(T, H, dv, dtype=torch.float64)
     Sa, na, ma = S0.double().clone(), n0.double().clone(), m0.double().clone()
     qd, kd, vd = (q.double() * dk ** -0.5).reshape(T, H, dk), k.double().reshape(T, H, dk), v.double().reshape(T, H, dv)
