@@ -15,7 +15,7 @@
 // Query and key heads may be shared by several value heads (head h reads q/k head h / (heads / qk_heads)).
 //
 // Both: a block owns some columns of S of one (row, head) and walks the row's tokens in order; a column lives in the
-// registers of L = 4 or 8 neighbouring lanes (rows i = L r + lane % L), the two dot products of a token are summed
+// registers of L = 4 or 8 neighbouring lanes (a lane holds NR rows in a row, i = NR (lane % L) + r), the two dot products of a token are summed
 // inside those lanes; q, k, the decays, the block's values and the tokens' scalars are staged in shared memory a chunk of
 // tokens at a time (the gates' exponentials of a chunk side by side, only the running maximum in order), so that a
 // token's step reads shared memory only and a chunk's load latency is paid once.
@@ -95,8 +95,17 @@ struct MatrixMemoryArgs {
 // maximum m_run (mode 0) is carried by every thread alike.  Ends with a barrier.
 template <int MODE>
 __device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, int h, int qh, int j0, float* sq, float* sk,
-                                      float* sg, float* sv, float* sc, float* sgate, float& m_run) {
+                                      float* sg, float* sv, float* sc, float* sgate, float& m_run, int ln) {
   const int dk = g.dk, dv = g.dv;
+  if (ln > dk) {                                    // rows beyond the key's features: keys of zero, decays of one
+    const int pad = ln - dk;
+    for (int e = threadIdx.x; e < n * pad; e += blockDim.x) {
+      const int tt = e / pad, i = dk + e - tt * pad;
+      sq[tt * ln + i] = 0.0f;
+      sk[tt * ln + i] = 0.0f;
+      if (MODE == 1) sg[tt * ln + i] = 1.0f;
+    }
+  }
   if (g.vec) {
     // rows of q, k (and the decays' pre-activations) in 16-byte pieces, four pieces of each in flight a thread
     const int per = dk / 4;                           // pieces of four features in a token's row
@@ -121,9 +130,9 @@ __device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, 
           const int tt = e / per, i = (e - tt * per) * 4;
 #pragma unroll
           for (int c = 0; c < 4; ++c) {
-            sq[tt * dk + i + c] = vq[u][c] * g.q_scale;
-            sk[tt * dk + i + c] = vk[u][c];
-            if (MODE == 1) sg[tt * dk + i + c] = expf(-ea * mm_softplus(va[u][c] + __ldg(g.dt_bias + h * dk + i + c)));
+            sq[tt * ln + i + c] = vq[u][c] * g.q_scale;
+            sk[tt * ln + i + c] = vk[u][c];
+            if (MODE == 1) sg[tt * ln + i + c] = expf(-ea * mm_softplus(va[u][c] + __ldg(g.dt_bias + h * dk + i + c)));
           }
         }
       }
@@ -132,11 +141,11 @@ __device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, 
     for (int e = threadIdx.x; e < n * dk; e += blockDim.x) {
       const int tt = e / dk, i = e - tt * dk;
       const int64_t t = t0 + tt;
-      sq[e] = mm_load(g.q, g.qkv_dtype, t * g.ldq + (int64_t)qh * dk + i) * g.q_scale;
-      sk[e] = mm_load(g.k, g.qkv_dtype, t * g.ldk + (int64_t)qh * dk + i);
+      sq[tt * ln + i] = mm_load(g.q, g.qkv_dtype, t * g.ldq + (int64_t)qh * dk + i) * g.q_scale;
+      sk[tt * ln + i] = mm_load(g.k, g.qkv_dtype, t * g.ldk + (int64_t)qh * dk + i);
       if (MODE == 1) {
         const float za = mm_load(g.za, g.za_dtype, t * g.ld_za + (int64_t)h * dk + i) + __ldg(g.dt_bias + h * dk + i);
-        sg[e] = expf(-expf(__ldg(g.a_log + h)) * mm_softplus(za));
+        sg[tt * ln + i] = expf(-expf(__ldg(g.a_log + h)) * mm_softplus(za));
       }
     }
   }
@@ -190,12 +199,13 @@ __device__ inline void mm_stage_chunk(const MatrixMemoryArgs& g, int t0, int n, 
 // memory column by column, [dv][dk], so that the lanes of a column read and write neighbouring addresses.
 template <int MODE, int L, int NR>
 __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemoryArgs g, int chunk) {
-  extern __shared__ float sm[];                      // q, k, (g) [chunk][dk]; v [chunk][MM_COLS]; scalars [chunk][4]; gates [chunk][2]
+  extern __shared__ __align__(16) float sm[];        // q, k, (g) [chunk][LN]; v [chunk][MM_COLS]; scalars [chunk][4]; gates [chunk][2]
+  constexpr int LN = L * NR;                         // a token's vectors padded to the rows the lanes hold
   const int dk = g.dk, dv = g.dv;
   float* sq = sm;
-  float* sk = sq + chunk * dk;
-  float* sg = sk + chunk * dk;
-  float* sv = sg + (MODE == 1 ? chunk * dk : 0);
+  float* sk = sq + chunk * LN;
+  float* sg = sk + chunk * LN;
+  float* sv = sg + (MODE == 1 ? chunk * LN : 0);
   float* sc = sv + chunk * MM_COLS;
   float* sgate = sc + chunk * 4;
   const int phase = MODE == 0 ? g.phase : 0;
@@ -223,7 +233,7 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
   }
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
-    const int i = r * L + lane4;
+    const int i = lane4 * NR + r;
     S[r] = 0.0f;
     nn[r] = 0.0f;
     if (phase == 2) {
@@ -241,7 +251,7 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
     if (piece == 0) {                                // the states as the step found them, for the third kernel
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
-        const int i = r * L + lane4;
+        const int i = lane4 * NR + r;
         if (col_ok && i < dk) init[(int64_t)j * dk + i] = S[r];
         if (blockIdx.z == 0 && col == 0 && i < dk) init[dv * dk + i] = nn[r];
         S[r] = 0.0f;                                 // a summary starts from nothing
@@ -254,52 +264,77 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
   float m_run = (MODE == 0 && phase == 0) ? g.m_state[(int64_t)slot * g.H + h] : 0.0f;
   for (int c0 = t0; c0 < t1; c0 += chunk) {
     const int n = min(chunk, t1 - c0);
-    mm_stage_chunk<MODE>(g, c0, n, h, qh, j0, sq, sk, sg, sv, sc, sgate, m_run);
+    mm_stage_chunk<MODE>(g, c0, n, h, qh, j0, sq, sk, sg, sv, sc, sgate, m_run, LN);
     for (int tt = 0; tt < n; ++tt) {
-      const float* q_ = sq + tt * dk;
-      const float* k_ = sk + tt * dk;
+      // this lane's rows of the token's vectors, 16 bytes at a time (the padding makes every row valid)
+      const float4* q4 = reinterpret_cast<const float4*>(sq + tt * LN + lane4 * NR);
+      const float4* k4 = reinterpret_cast<const float4*>(sk + tt * LN + lane4 * NR);
       const float vj = sv[tt * MM_COLS + col];
-      float o;
+      float o = 0.0f;
       if (MODE == 0) {
         const float a = sc[tt * 4], bw = sc[tt * 4 + 1];
         const float bv = bw * vj;
         decay *= a;
-        float num = 0.0f, nq = 0.0f;
+        if (phase == 1) {                              // a summary needs no read-out
 #pragma unroll
-        for (int r = 0; r < NR; ++r) {
-          const int i = r * L + lane4;
-          const float kk = i < dk ? k_[i] : 0.0f, qq = i < dk ? q_[i] : 0.0f;
-          S[r] = fmaf(a, S[r], kk * bv);
-          nn[r] = fmaf(a, nn[r], bw * kk);
-          num = fmaf(S[r], qq, num);
-          nq = fmaf(nn[r], qq, nq);
-        }
+          for (int r4 = 0; r4 < NR / 4; ++r4) {
+            const float4 kk = k4[r4];
+            const float kv[4] = {kk.x, kk.y, kk.z, kk.w};
 #pragma unroll
-        for (int o2 = 1; o2 < L; o2 <<= 1) {
-          num += __shfl_xor_sync(0xffffffffu, num, o2);
-          nq += __shfl_xor_sync(0xffffffffu, nq, o2);
+            for (int c = 0; c < 4; ++c) {
+              S[r4 * 4 + c] = fmaf(a, S[r4 * 4 + c], kv[c] * bv);
+              nn[r4 * 4 + c] = fmaf(a, nn[r4 * 4 + c], bw * kv[c]);
+            }
+          }
+        } else {
+          float num = 0.0f, nq = 0.0f;
+#pragma unroll
+          for (int r4 = 0; r4 < NR / 4; ++r4) {
+            const float4 kk = k4[r4], qq = q4[r4];
+            const float kv[4] = {kk.x, kk.y, kk.z, kk.w}, qv[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              S[r4 * 4 + c] = fmaf(a, S[r4 * 4 + c], kv[c] * bv);
+              nn[r4 * 4 + c] = fmaf(a, nn[r4 * 4 + c], bw * kv[c]);
+              num = fmaf(S[r4 * 4 + c], qv[c], num);
+              nq = fmaf(nn[r4 * 4 + c], qv[c], nq);
+            }
+          }
+#pragma unroll
+          for (int o2 = 1; o2 < L; o2 <<= 1) {
+            num += __shfl_xor_sync(0xffffffffu, num, o2);
+            nq += __shfl_xor_sync(0xffffffffu, nq, o2);
+          }
+          o = __fdividef(num, fmaxf(fabsf(nq), sc[tt * 4 + 2]) + 1e-6f);
         }
-        o = __fdividef(num, fmaxf(fabsf(nq), sc[tt * 4 + 2]) + 1e-6f);
       } else {
-        const float* g_ = sg + tt * dk;
+        const float4* g4 = reinterpret_cast<const float4*>(sg + tt * LN + lane4 * NR);
+        float kr[NR];
         float dot = 0.0f;
 #pragma unroll
-        for (int r = 0; r < NR; ++r) {
-          const int i = r * L + lane4;
-          const float gg = i < dk ? g_[i] : 1.0f, kk = i < dk ? k_[i] : 0.0f;
-          S[r] *= gg;
-          dot = fmaf(S[r], kk, dot);
+        for (int r4 = 0; r4 < NR / 4; ++r4) {
+          const float4 gg = g4[r4], kk = k4[r4];
+          const float gv[4] = {gg.x, gg.y, gg.z, gg.w}, kv[4] = {kk.x, kk.y, kk.z, kk.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            kr[r4 * 4 + c] = kv[c];
+            S[r4 * 4 + c] *= gv[c];
+            dot = fmaf(S[r4 * 4 + c], kv[c], dot);
+          }
         }
 #pragma unroll
         for (int o2 = 1; o2 < L; o2 <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, o2);
         const float u = sc[tt * 4 + 3] * (vj - dot);
         float num = 0.0f;
 #pragma unroll
-        for (int r = 0; r < NR; ++r) {
-          const int i = r * L + lane4;
-          const float kk = i < dk ? k_[i] : 0.0f, qq = i < dk ? q_[i] : 0.0f;
-          S[r] = fmaf(kk, u, S[r]);
-          num = fmaf(S[r], qq, num);
+        for (int r4 = 0; r4 < NR / 4; ++r4) {
+          const float4 qq = q4[r4];
+          const float qv[4] = {qq.x, qq.y, qq.z, qq.w};
+#pragma unroll
+          for (int c = 0; c < 4; ++c) {
+            S[r4 * 4 + c] = fmaf(kr[r4 * 4 + c], u, S[r4 * 4 + c]);
+            num = fmaf(S[r4 * 4 + c], qv[c], num);
+          }
         }
 #pragma unroll
         for (int o2 = 1; o2 < L; o2 <<= 1) num += __shfl_xor_sync(0xffffffffu, num, o2);
@@ -313,7 +348,7 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
     float* sm_c = g.sums + (((int64_t)row * g.pieces + piece) * g.H + h) * rec;
 #pragma unroll
     for (int r = 0; r < NR; ++r) {
-      const int i = r * L + lane4;
+      const int i = lane4 * NR + r;
       if (col_ok && i < dk) sm_c[(int64_t)j * dk + i] = S[r];
       if (blockIdx.z == 0 && col == 0 && i < dk) sm_c[dv * dk + i] = nn[r];
     }
@@ -323,7 +358,7 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
   if (phase == 2 && t1 < row_end) return;            // only a row's last piece holds the row's last state
 #pragma unroll
   for (int r = 0; r < NR; ++r) {
-    const int i = r * L + lane4;
+    const int i = lane4 * NR + r;
     if (col_ok && i < dk) Sp[(int64_t)j * dk + i] = S[r];
     // the normaliser and the maximum are the same in every block of a head: the first block's first column writes them
     if (MODE == 0 && blockIdx.z == 0 && col == 0 && i < dk)
@@ -403,7 +438,12 @@ __global__ void __launch_bounds__(256) mlstm_fold_kernel(MatrixMemoryArgs g) {
 }
 
 template <int MODE, int L, int NR>
-static int mm_launch_nr(const MatrixMemoryArgs& g, dim3 grid, int chunk, size_t smem, cudaStream_t stream) {
+static int mm_launch_nr(const MatrixMemoryArgs& g, dim3 grid, int max_new, cudaStream_t stream) {
+  // tokens staged at once: as many as a row brings, up to MM_CHUNK (at most as many as the block has threads) and to
+  // what fits 96 KB of shared memory
+  const size_t per_token = (size_t)((MODE == 1 ? 3 : 2) * L * NR + MM_COLS + 6) * sizeof(float);
+  const int chunk = max(1, min(min(max_new, MM_CHUNK), (int)(96 * 1024 / per_token)));
+  const size_t smem = (size_t)chunk * per_token;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(matrix_memory_kernel<MODE, L, NR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) { set_error("matrix_memory: %zu bytes of shared memory refused: %s", smem, cudaGetErrorString(e)); return (int)e; }
@@ -416,27 +456,22 @@ template <int MODE>
 static int mm_launch(const MatrixMemoryArgs& g, int rows, int max_new, cudaStream_t stream) {
   const dim3 grid(g.phase ? rows * g.pieces : rows, g.H, ceil_div(g.dv, MM_COLS));
   if (g.phase) max_new = g.piece_len;
-  // tokens staged at once: as many as a row brings, up to MM_CHUNK (at most as many as the block has threads) and to
-  // what fits 96 KB of shared memory
-  const size_t per_token = (size_t)((MODE == 1 ? 3 : 2) * g.dk + MM_COLS + 6) * sizeof(float);
-  const int chunk = max(1, min(min(max_new, MM_CHUNK), (int)(96 * 1024 / per_token)));
-  const size_t smem = (size_t)chunk * per_token;
   // Eight lanes a column from keys of 32 features on: twice the warps of four lanes a column to hide each other's
   // waits, half the rows a lane walks for every token.  (Sixteen lanes a column were measured and lose: what a token
   // costs a warp beyond its rows, the sums across lanes, the division, the store, is then paid by twice the warps, and
   // the kernel is bound by the instructions it issues.)
-  if (g.dk < 32) return mm_launch_nr<MODE, 4, 8>(g, grid, chunk, smem, stream);
+  if (g.dk < 32) return mm_launch_nr<MODE, 4, 8>(g, grid, max_new, stream);
   if (g.phase && g.dk <= 128) {
     // pieces side by side fill the SMs with blocks: four lanes a column then cost the fewest instructions a column
     const int nr4 = ceil_div(g.dk, 4);
-    if (nr4 <= 16) return mm_launch_nr<MODE, 4, 16>(g, grid, chunk, smem, stream);
-    return mm_launch_nr<MODE, 4, 32>(g, grid, chunk, smem, stream);
+    if (nr4 <= 16) return mm_launch_nr<MODE, 4, 16>(g, grid, max_new, stream);
+    return mm_launch_nr<MODE, 4, 32>(g, grid, max_new, stream);
   }
   const int nr = ceil_div(g.dk, 8);
-  if (nr <= 4) return mm_launch_nr<MODE, 8, 4>(g, grid, chunk, smem, stream);
-  if (nr <= 8) return mm_launch_nr<MODE, 8, 8>(g, grid, chunk, smem, stream);
-  if (nr <= 16) return mm_launch_nr<MODE, 8, 16>(g, grid, chunk, smem, stream);
-  if (nr <= 32) return mm_launch_nr<MODE, 8, 32>(g, grid, chunk, smem, stream);
+  if (nr <= 4) return mm_launch_nr<MODE, 8, 4>(g, grid, max_new, stream);
+  if (nr <= 8) return mm_launch_nr<MODE, 8, 8>(g, grid, max_new, stream);
+  if (nr <= 16) return mm_launch_nr<MODE, 8, 16>(g, grid, max_new, stream);
+  if (nr <= 32) return mm_launch_nr<MODE, 8, 32>(g, grid, max_new, stream);
   set_error("matrix_memory: keys of %d features are too wide (at most 256)", g.dk);
   return ERR_UNSUPPORTED;
 }
