@@ -185,9 +185,9 @@ def potodra_config(z):
     plain = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": hd, "vdim": hd, "scale": hd ** -0.5,
              "rot": {"base": 500000.0, "dims": hd}, "softcap": None, "mask": None}
     att = dict(plain, softcap=30.0, mask={"size": 1024, "keep_first": 64})
-    memory = {"heads": z["heads"], "dim": 64, "vdim": hd, "gate_cap": 15.0}
+    memory = {"heads": z["heads"], "dim": 64, "vdim": hd, "gate_cap": 12.0}
     delta = {"heads": z["heads"], "kv_heads": z["kv_heads"], "dim": 64, "vdim": hd, "conv": 4}
-    par = {"left": plain, "right": delta, "left_scale": 0.6, "right_scale": 0.5}
+    par = {"left": plain, "right": delta, "left_scale": 0.7, "right_scale": 0.4}
     dense = {"kind": "dense", "ff": z["ff"]}
     moe = {"kind": "moe", "expert": {"ff": z["ff"] // 4, "limit": 7.0}, "shared": {"ff": z["ff"] // 4, "limit": 7.0},
            "router": {"experts": 16, "top": 2, "groups": {"count": 4, "keep": 2}}}

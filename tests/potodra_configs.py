@@ -81,10 +81,10 @@ CONFIGS = {
     # attention, keys of 64 and 128 in the recurrences, a window of three pages that keeps one page exactly
     "wide": cfg(301, 128, 4, 1e-5, 4.0, [
         L("parallel", par(attn(4, 2, 64, 64, 0.11), delta(2, 1, 64, 64, 4), 0.5, 0.5), dense(192)),
-        L("attention", attn(4, 1, 64, 64, 0.12, window=192, keep=64, softcap=15.0), moe(64, 1.5, 8, 2, groups=(4, 2), shared=(64, 1.5))),
+        L("attention", attn(4, 1, 64, 64, 0.12, window=192, keep=64, softcap=15.0), moe(64, 1.75, 8, 2, groups=(4, 2), shared=(64, 1.25))),
         L("mlstm", mlstm(2, 128, 64, 12.0), dense(128)),
         L("parallel", par(attn(2, 2, 128, 128, 0.08, dims=64), delta(2, 2, 128, 32, 4), 0.9, 0.2), None),
-        L("mlstm", mlstm(2, 64, 128, 15.0), None),
+        L("mlstm", mlstm(2, 64, 128, 14.0), None),
     ]),
     # each mechanism alone
     "only_attention": cfg(128, 64, 4, 1e-5, 2.0, [L("attention", attn(4, 2, 32, 16, 0.25, window=70, keep=9, softcap=12.0, dims=16), None)]),
@@ -109,7 +109,7 @@ def random_config(seed: int) -> PotodraConfig:
         window = r.choice([1, 2, 5, 31, 64, 65, 200]) if windowed and r.random() < 0.8 else None
         return attn(kv * r.randint(1, 4), kv, dim, r.choice([8, 12, 16, 32, 64]), r.uniform(0.1, 0.3), window=window,
                     keep=r.choice([0, 1, 3, 64, 100]) if window else 0,
-                    softcap=r.choice([None, 5.0, 20.0, 50.0]) if windowed else None,
+                    softcap=r.choice([None, 5.0, 25.0, 50.0]) if windowed else None,
                     base=r.choice([100.0, 10000.0, 1e6]), dims=r.choice([0, 2, dim // 2 * 2, dim]))
 
     layers = []
@@ -119,7 +119,7 @@ def random_config(seed: int) -> PotodraConfig:
             mixer = an_attention(True)
         elif kind == "mlstm":
             mixer = mlstm(r.randint(1, 4), r.choice([4, 8, 12, 16, 32, 40]), r.choice([6, 8, 16, 24, 32]),
-                          r.choice([2.0, 10.0, 15.0, 30.0]))
+                          r.choice([2.0, 10.0, 12.0, 30.0]))
         else:
             g = r.randint(1, 2)
             mixer = par(an_attention(False), delta(g * r.randint(1, 3), g, r.choice([4, 8, 12, 16, 32]),
@@ -133,7 +133,7 @@ def random_config(seed: int) -> PotodraConfig:
         else:
             per, groups = r.randint(1, 4), r.randint(1, 4)
             keep = r.randint(1, groups)
-            mlp = moe(r.choice([8, 24, 40]), r.choice([0.7, 1.5, 7.0]), per * groups, r.randint(1, keep * per),
+            mlp = moe(r.choice([8, 24, 40]), r.choice([0.7, 1.3, 7.0]), per * groups, r.randint(1, keep * per),
                       groups=(groups, keep), shared=r.choice([None, (16, 1.0), (40, 3.0)]))
         layers.append(L(kind, mixer, mlp))
     return cfg(r.randint(40, 300), width, r.randint(1, 5), r.choice([1e-6, 1e-5, 1e-4]), r.uniform(0.5, 4.0), layers)
