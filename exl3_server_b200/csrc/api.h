@@ -374,7 +374,9 @@ size_t exl3_mlstm_scan_scratch_bytes(int rows, int T, int heads, int dk, int dv,
 int exl3_delta_scan(const void* q, int64_t ldq, const void* k, int64_t ldk, const void* v, int64_t ldv, int qkv_dtype,
                     const void* zb, int zb_dtype, int64_t ld_zb, const void* za, int za_dtype, int64_t ld_za,
                     const float* a_log, const float* dt_bias, float* s_state, const int* slot_ids, const int* row_start,
-                    float* out, int rows, int T, int heads, int qk_heads, int dk, int dv, int max_new, cudaStream_t stream);
+                    float* out, int rows, int T, int heads, int qk_heads, int dk, int dv, int max_new, float* scratch,
+                    size_t scratch_bytes, cudaStream_t stream);
+size_t exl3_delta_scan_scratch_bytes(int rows, int T, int heads, int dk, int dv, int max_new);
 // Short causal convolution per channel, SiLU, unit q and k heads (see matrix_memory.cu).  out float32 [T, 2 qk_heads dk +
 // v_heads dv]; state float32 [slots, channels, n_taps - 1].
 int exl3_conv_prep_max_taps();

@@ -20,6 +20,11 @@
 // tokens at a time (the gates' exponentials of a chunk side by side, only the running maximum in order), so that a
 // token's step reads shared memory only and a chunk's load latency is paid once.
 //
+// Mode 1 for prompts: a token multiplies the state by (I - beta k k^T) diag(g) and adds beta k v^T, so a piece of tokens
+// multiplies the state it finds by a matrix T [dk x dk] and adds what it leaves from a zero state.  The summaries' kernel
+// gets T by walking dk more columns that start as the identity with values of zero; a fold (delta_fold_kernel) takes
+// S <- T S + B through a row's pieces in order; the outputs' kernel starts every piece from the state before it.
+//
 // Mode 0 for prompts: between two tokens the state only decays by one number a head (a = exp(f + m - m')) once the
 // running maxima are known, so a row is cut into pieces that run side by side.  A first kernel walks the gates of a row
 // in order and leaves a, b = exp(i - m') and exp(-m') per token; a second walks every piece but a row's last from a
@@ -208,14 +213,17 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
   float* sv = sg + (MODE == 1 ? chunk * LN : 0);
   float* sc = sv + chunk * MM_COLS;
   float* sgate = sc + chunk * 4;
-  const int phase = MODE == 0 ? g.phase : 0;
+  const int phase = g.phase;
   const int row = phase ? blockIdx.x / g.pieces : blockIdx.x, piece = phase ? blockIdx.x - row * g.pieces : 0;
   const int h = blockIdx.y, j0 = blockIdx.z * MM_COLS;
   const int qh = h / (g.H / g.QH);
   const int lane4 = threadIdx.x & (L - 1);          // this lane's place among the lanes of its column
   const int col = threadIdx.x / L;
   const int j = j0 + col;
-  const bool col_ok = j < dv;
+  // Mode 1, phase 1: dk more columns behind the values' own.  They start as the identity and get values of zero, so
+  // they end as the matrix that the piece's tokens multiply a state by (the step is linear in the state).
+  const bool t_col = MODE == 1 && phase == 1 && j >= dv && j < dv + dk;
+  const bool col_ok = j < dv || t_col;
   pdl_wait();
   pdl_trigger();
   int t0 = __ldcg(g.row_start + row), t1 = __ldcg(g.row_start + row + 1);
@@ -224,8 +232,9 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
   float* Sp = g.s_state + ((int64_t)slot * g.H + h) * dk * dv;
   float S[NR], nn[NR];
   const int row_end = t1;
-  const int rec = dv * dk + dk + 1;                  // floats of a piece's summary
-  float* init = phase ? g.init + ((int64_t)row * g.H + h) * (dv * dk + dk) : nullptr;
+  // floats of a piece's summary: mode 0 S, n and the piece's decay; mode 1 S and the dk columns of the piece's matrix
+  const int rec = MODE == 0 ? dv * dk + dk + 1 : (dv + dk) * dk;
+  float* init = phase ? g.init + ((int64_t)row * g.H + h) * (MODE == 0 ? dv * dk + dk : dv * dk) : nullptr;
   if (phase) {                                       // this block's piece of the row
     t0 += piece * g.piece_len;
     if (t0 >= t1) return;
@@ -241,9 +250,9 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
       // summary of the piece before
       const float* from = piece == 0 ? init : g.sums + (((int64_t)row * g.pieces + piece - 1) * g.H + h) * rec;
       if (col_ok && i < dk) S[r] = __ldcg(from + (int64_t)j * dk + i);
-      if (i < dk) nn[r] = __ldcg(from + dv * dk + i);
+      if (MODE == 0 && i < dk) nn[r] = __ldcg(from + dv * dk + i);
     } else if (phase == 0 || piece == 0) {
-      if (col_ok && i < dk) S[r] = Sp[(int64_t)j * dk + i];
+      if (j < dv && i < dk) S[r] = Sp[(int64_t)j * dk + i];
       if (MODE == 0 && i < dk) nn[r] = g.n_state[((int64_t)slot * g.H + h) * dk + i];
     }
   }
@@ -252,13 +261,17 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
 #pragma unroll
       for (int r = 0; r < NR; ++r) {
         const int i = lane4 * NR + r;
-        if (col_ok && i < dk) init[(int64_t)j * dk + i] = S[r];
-        if (blockIdx.z == 0 && col == 0 && i < dk) init[dv * dk + i] = nn[r];
+        if (j < dv && i < dk) init[(int64_t)j * dk + i] = S[r];
+        if (MODE == 0 && blockIdx.z == 0 && col == 0 && i < dk) init[dv * dk + i] = nn[r];
         S[r] = 0.0f;                                 // a summary starts from nothing
         nn[r] = 0.0f;
       }
     }
     if (t1 >= row_end) return;                       // nobody needs the summary of a row's last piece
+    if (t_col) {
+#pragma unroll
+      for (int r = 0; r < NR; ++r) S[r] = (lane4 * NR + r == j - dv) ? 1.0f : 0.0f;
+    }
   }
   float decay = 1.0f;                                // the piece's whole decay (phase 1)
   float m_run = (MODE == 0 && phase == 0) ? g.m_state[(int64_t)slot * g.H + h] : 0.0f;
@@ -350,9 +363,9 @@ __global__ void __launch_bounds__(L * MM_COLS) matrix_memory_kernel(MatrixMemory
     for (int r = 0; r < NR; ++r) {
       const int i = lane4 * NR + r;
       if (col_ok && i < dk) sm_c[(int64_t)j * dk + i] = S[r];
-      if (blockIdx.z == 0 && col == 0 && i < dk) sm_c[dv * dk + i] = nn[r];
+      if (MODE == 0 && blockIdx.z == 0 && col == 0 && i < dk) sm_c[dv * dk + i] = nn[r];
     }
-    if (blockIdx.z == 0 && threadIdx.x == 0) sm_c[dv * dk + dk] = decay;
+    if (MODE == 0 && blockIdx.z == 0 && threadIdx.x == 0) sm_c[dv * dk + dk] = decay;
     return;
   }
   if (phase == 2 && t1 < row_end) return;            // only a row's last piece holds the row's last state
@@ -437,6 +450,51 @@ __global__ void __launch_bounds__(256) mlstm_fold_kernel(MatrixMemoryArgs g) {
   }
 }
 
+// The delta rule's fold: a piece multiplies the state it finds by a matrix T [dk x dk] and adds its own end from zero,
+// S <- T S + B.  A block takes four columns of a (row, head)'s state through the row's pieces in order (a column in
+// shared memory, a thread an element: dk multiply-adds a piece) and leaves the state after every piece in the piece's
+// summary, where the next piece starts.
+constexpr int DF_COLS = 4;
+__global__ void __launch_bounds__(1024) delta_fold_kernel(MatrixMemoryArgs g) {
+  extern __shared__ float scol[];                    // [DF_COLS][dk]
+  pdl_wait();
+  pdl_trigger();
+  const int dk = g.dk, dv = g.dv;
+  const int row = blockIdx.x, h = blockIdx.y;
+  const int jl = threadIdx.x / dk, i = threadIdx.x - jl * dk;
+  const int j = blockIdx.z * DF_COLS + jl;
+  const int n = __ldcg(g.row_start + row + 1) - __ldcg(g.row_start + row);
+  const int summaries = (n + g.piece_len - 1) / g.piece_len - 1;
+  if (summaries < 1) return;
+  const bool ok = jl < DF_COLS && j < dv;
+  const int rec = (dv + dk) * dk;
+  float s = ok ? __ldcg(g.init + ((int64_t)row * g.H + h) * dv * dk + (int64_t)j * dk + i) : 0.0f;
+  for (int c = 0; c < summaries; ++c) {
+    float* sm_c = g.sums + (((int64_t)row * g.pieces + c) * g.H + h) * rec;
+    if (ok) scol[jl * dk + i] = s;
+    __syncthreads();
+    if (ok) {
+      const float* T = sm_c + (int64_t)dv * dk;      // column m of the matrix at T + m dk
+      float a0 = __ldcg(sm_c + (int64_t)j * dk + i), a1 = 0.0f;
+      int m = 0;
+      for (; m + 16 <= dk; m += 16) {                // sixteen of the matrix's elements in flight before the first is used
+        float tv[16];
+#pragma unroll
+        for (int u = 0; u < 16; ++u) tv[u] = __ldcg(T + (int64_t)(m + u) * dk + i);
+#pragma unroll
+        for (int u = 0; u < 16; u += 2) {
+          a0 = fmaf(tv[u], scol[jl * dk + m + u], a0);
+          a1 = fmaf(tv[u + 1], scol[jl * dk + m + u + 1], a1);
+        }
+      }
+      for (; m < dk; ++m) a0 = fmaf(__ldcg(T + (int64_t)m * dk + i), scol[jl * dk + m], a0);
+      s = a0 + a1;
+    }
+    __syncthreads();                                 // everyone has read the matrix's rows and the old column
+    if (ok) sm_c[(int64_t)j * dk + i] = s;
+  }
+}
+
 template <int MODE, int L, int NR>
 static int mm_launch_nr(const MatrixMemoryArgs& g, dim3 grid, int max_new, cudaStream_t stream) {
   // tokens staged at once: as many as a row brings, up to MM_CHUNK (at most as many as the block has threads) and to
@@ -454,7 +512,7 @@ static int mm_launch_nr(const MatrixMemoryArgs& g, dim3 grid, int max_new, cudaS
 
 template <int MODE>
 static int mm_launch(const MatrixMemoryArgs& g, int rows, int max_new, cudaStream_t stream) {
-  const dim3 grid(g.phase ? rows * g.pieces : rows, g.H, ceil_div(g.dv, MM_COLS));
+  const dim3 grid(g.phase ? rows * g.pieces : rows, g.H, ceil_div(g.dv + (MODE == 1 && g.phase == 1 ? g.dk : 0), MM_COLS));
   if (g.phase) max_new = g.piece_len;
   // Eight lanes a column from keys of 32 features on: twice the warps of four lanes a column to hide each other's
   // waits, half the rows a lane walks for every token.  (Sixteen lanes a column were measured and lose: what a token
@@ -587,6 +645,25 @@ static size_t mlstm_pieces(int rows, int T, int heads, int dk, int dv, int max_n
   return ((size_t)T * heads * 4 + (size_t)rows * heads * ((size_t)dv * dk + dk) + (size_t)rows * *pieces * heads * rec) * sizeof(float);
 }
 
+// The same for the delta rule, whose pieces' summaries also hold the piece's matrix (dk more columns); keys of up to 256
+// features (the fold's block is four columns of dk threads).
+static size_t delta_pieces(int rows, int T, int heads, int dk, int dv, int max_new, int* piece_len, int* pieces) {
+  if (max_new < MLSTM_MIN_PIECED || dk > 256) return 0;
+  // The pieces cost the walk in order two and a half times over (dk more columns for the matrices, the fold, the second
+  // walk), so they pay only while the walk in order would leave most of the GPU idle: measured even at 64 blocks in
+  // order (16 heads of 128 values: 0.91 against 1.01 ms for 2,048 tokens), behind at 128 (32 heads).
+  if ((int64_t)rows * heads * exl3::ceil_div(dv, exl3::MM_COLS) > 64) return 0;
+  const int len = 64 * exl3::ceil_div(exl3::ceil_div(T, 64), 64);
+  *piece_len = len < 64 ? 64 : len;
+  *pieces = exl3::ceil_div(max_new, *piece_len);
+  return ((size_t)rows * heads * dv * dk + (size_t)rows * *pieces * heads * ((size_t)dv + dk) * dk) * sizeof(float);
+}
+
+extern "C" size_t exl3_delta_scan_scratch_bytes(int rows, int T, int heads, int dk, int dv, int max_new) {
+  int a = 0, b = 0;
+  return delta_pieces(rows, T, heads, dk, dv, max_new, &a, &b);
+}
+
 extern "C" size_t exl3_mlstm_scan_scratch_bytes(int rows, int T, int heads, int dk, int dv, int max_new) {
   int a = 0, b = 0;
   return mlstm_pieces(rows, T, heads, dk, dv, max_new, &a, &b);
@@ -641,7 +718,8 @@ extern "C" int exl3_delta_scan(const void* q, int64_t ldq, const void* k, int64_
                                int qkv_dtype, const void* zb, int zb_dtype, int64_t ld_zb, const void* za, int za_dtype,
                                int64_t ld_za, const float* a_log, const float* dt_bias, float* s_state,
                                const int* slot_ids, const int* row_start, float* out, int rows, int T, int heads,
-                               int qk_heads, int dk, int dv, int max_new, cudaStream_t stream) {
+                               int qk_heads, int dk, int dv, int max_new, float* scratch, size_t scratch_bytes,
+                               cudaStream_t stream) {
   if (T == 0 || rows == 0) return 0;
   if (T < 0 || rows < 0 || max_new < 1 || heads < 1 || qk_heads < 1 || heads % qk_heads != 0 || dk < 1 || dv < 1 || !mm_dtype_ok(qkv_dtype) ||
       !mm_dtype_ok(zb_dtype) || !mm_dtype_ok(za_dtype) || heads > 65535 || dv > 65535 * MM_COLS) {
@@ -655,6 +733,25 @@ extern "C" int exl3_delta_scan(const void* q, int64_t ldq, const void* k, int64_
   g.out = out; g.H = heads; g.QH = qk_heads; g.dk = dk; g.dv = dv;
   g.vec = dk % 4 == 0 && ldq % 4 == 0 && ldk % 4 == 0 && ld_za % 4 == 0 && mm_aligned(q, qkv_dtype) &&
           mm_aligned(k, qkv_dtype) && mm_aligned(za, za_dtype);
+  int piece_len = 0, pieces = 0;
+  const size_t need = delta_pieces(rows, T, heads, dk, dv, max_new, &piece_len, &pieces);
+  if (need == 0) return mm_launch<1>(g, rows, max_new, stream);
+  if (scratch == nullptr || scratch_bytes < need || !aligned16(scratch)) {
+    set_error("delta_scan: rows of up to %d tokens need %zu bytes of 16-byte aligned scratch, got %zu", max_new, need, scratch_bytes);
+    return ERR_SCRATCH;
+  }
+  g.init = scratch;
+  g.sums = g.init + (size_t)rows * heads * dv * dk;
+  g.piece_len = piece_len;
+  g.pieces = pieces;
+  g.phase = 1;
+  int rc = mm_launch<1>(g, rows, max_new, stream);
+  if (rc) return rc;
+  launch_pdl(delta_fold_kernel, dim3(rows, heads, ceil_div(dv, DF_COLS)), dim3(DF_COLS * dk), (size_t)DF_COLS * dk * sizeof(float),
+             stream, g);
+  rc = launch_status("delta_fold");
+  if (rc) return rc;
+  g.phase = 2;
   return mm_launch<1>(g, rows, max_new, stream);
 }
 

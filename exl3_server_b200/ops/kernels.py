@@ -1407,14 +1407,23 @@ def mlstm_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zi: torch.Tens
     return out
 
 
+def delta_scan_scratch_bytes(rows: int, T: int, heads: int, dk: int, dv: int, max_new: int) -> int:
+    """Bytes of float32 scratch that ``delta_scan`` needs for a step (0 for steps of short rows, which run in order)."""
+    lib = library()
+    lib.exl3_delta_scan_scratch_bytes.restype = _c_size_t
+    return int(lib.exl3_delta_scan_scratch_bytes(_c_int(rows), _c_int(T), _c_int(heads), _c_int(dk), _c_int(dv),
+                                                 _c_int(max_new)))
+
+
 def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zb: torch.Tensor, za: torch.Tensor,
                a_log: torch.Tensor, dt_bias: torch.Tensor, s_state: torch.Tensor, slot_ids: torch.Tensor,
-               row_start: torch.Tensor, rows: int, heads: int, qk_heads: int, dk: int, dv: int, max_new: int) -> torch.Tensor:
+               row_start: torch.Tensor, rows: int, heads: int, qk_heads: int, dk: int, dv: int, max_new: int,
+               scratch: Optional[torch.Tensor] = None) -> torch.Tensor:
     """The gated delta rule over a step's packed tokens (see matrix_memory.cu): ``q``, ``k [T, qk_heads * dk]``,
     ``v [T, heads * dv]`` (one element type), ``zb [T, heads]`` (beta before its sigmoid), ``za [T, heads * dk]``
     (the decay's pre-activation, before ``dt_bias``), ``a_log [heads]``, ``dt_bias [heads * dk]`` float32; state
-    float32 ``[slots, heads, dv, dk]`` (the matrix column by column); ``max_new`` is the most tokens a row brings.
-    Returns float32 ``[T, heads * dv]``."""
+    float32 ``[slots, heads, dv, dk]`` (the matrix column by column); ``max_new`` is the most tokens a row brings; ``scratch``: float32 memory of
+    ``delta_scan_scratch_bytes`` bytes when that is not 0.  Returns float32 ``[T, heads * dv]``."""
     T = q.shape[0]
     for t, name in ((q, "q"), (k, "k"), (v, "v"), (zb, "zb"), (za, "za")):
         if t.stride(1) != 1:
@@ -1432,7 +1441,8 @@ def delta_scan(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, zb: torch.Tens
         _c_int(dtype_code(q.dtype)), _ptr(zb), _c_int(dtype_code(zb.dtype)), _c_int64(zb.stride(0)), _ptr(za),
         _c_int(dtype_code(za.dtype)), _c_int64(za.stride(0)), _ptr(a_log), _ptr(dt_bias), _ptr(s_state), _ptr(slot_ids),
         _ptr(row_start), _ptr(out), _c_int(rows), _c_int(T), _c_int(heads), _c_int(qk_heads), _c_int(dk), _c_int(dv),
-        _c_int(max_new), _stream()), "delta_scan")
+        _c_int(max_new), _ptr(scratch), _c_size_t(0 if scratch is None else scratch.numel() * scratch.element_size()),
+        _stream()), "delta_scan")
     return out
 
 

@@ -196,9 +196,10 @@ class GatedDelta:
                           batch.max_new)
         low = self.low(x, out_dtype=self.ctx.dtype)
         z = self.second(low, out_dtype=self.second.wide_dtype(T))
+        need = K.delta_scan_scratch_bytes(batch.n_rows, T, H, dk, dv, batch.max_new)
         o = K.delta_scan(qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], proj[:, b_off:b_off + H],
                          z[:, :H * dk], self.a_log, self.dt_bias, S, batch.slot_ids, batch.row_start, batch.n_rows,
-                         H, G, dk, dv, batch.max_new)
+                         H, G, dk, dv, batch.max_new, scratch=batch.workspace.plain(need // 4) if need else None)
         y = K.head_norm_gate(o, self.norm_w, z[:, H * dk:], self.eps, H, dv, self.ctx.dtype, gate_kind="sigmoid")
         return self.o(y, out_dtype=self.o.wide_dtype(T))
 

@@ -192,8 +192,10 @@ def test_mlstm_scan(dt, H, dk, dv, cap, lens):
 @pytest.mark.parametrize("dt", TYPES)
 @pytest.mark.parametrize("H, G, dk, dv", [(3, 1, 16, 8), (2, 2, 24, 16), (4, 2, 20, 12), (2, 1, 128, 32), (2, 2, 64, 130),
                                           (1, 1, 12, 20)])
-@pytest.mark.parametrize("lens", [[5, 1, 9], [150, 3, 64]])
+@pytest.mark.parametrize("lens", [[5, 1, 9], [150, 3, 64], [600, 2, 257]])
 def test_delta_scan(dt, H, G, dk, dv, lens):
+    """Rows of few tokens walk in order; with a row of 256 tokens or more the step runs as pieces of 64 tokens side by
+    side, joined through the pieces' matrices."""
     g = torch.Generator().manual_seed(8)
     k_ = K()
     slots = [4, 0, 6][:len(lens)]
@@ -208,8 +210,13 @@ def test_delta_scan(dt, H, G, dk, dv, lens):
     S0 = torch.randn(9, H, dk, dv, generator=g)
     S = S0.transpose(2, 3).contiguous().to(DEV)           # the kernel keeps S column by column
     qkv = torch.cat([q, k, v], dim=1).to(DEV)
+    need = k_.delta_scan_scratch_bytes(len(lens), T, H, dk, dv, max(lens))
+    assert (need > 0) == (max(lens) >= 256)          # these sizes are few blocks in order: long rows run as pieces
+    assert k_.delta_scan_scratch_bytes(8, 8 * 300, 16, 64, 128, 300) == 0      # many blocks in order: no pieces
+    scratch = torch.full((need // 4 + 4,), float("nan"), device=DEV)[:need // 4] if need else None
     out = k_.delta_scan(qkv[:, :G * dk], qkv[:, G * dk:2 * G * dk], qkv[:, 2 * G * dk:], zb.to(DEV)[:, 2:2 + H],
-                        za.to(DEV)[:, :H * dk], a_log.to(DEV), dt_bias.to(DEV), S, slot_ids, row_start, len(lens), H, G, dk, dv, max(lens))
+                        za.to(DEV)[:, :H * dk], a_log.to(DEV), dt_bias.to(DEV), S, slot_ids, row_start, len(lens), H, G, dk, dv,
+                        max(lens), scratch=scratch)
     want = torch.zeros(T, H, dv, dtype=torch.float64)
     Sa = S0.double().clone()
     qd, kd, vd = q.double().reshape(T, G, dk), k.double().reshape(T, G, dk), v.double().reshape(T, H, dv)
