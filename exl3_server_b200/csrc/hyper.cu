@@ -16,7 +16,7 @@
 
 namespace exl3 {
 
-constexpr int HC_MAX_STREAMS = 8;
+constexpr int HC_MAX_STREAMS = 16;      // the kernels are built for up to 4, 8 and 16 streams (MS)
 constexpr int HC_THREADS = 256;
 
 struct HyperArgs {
@@ -39,10 +39,11 @@ __device__ inline float hc_load(const void* p, int dtype, int64_t i) {
                          : __bfloat162float(__ldcg(static_cast<const __nv_bfloat16*>(p) + i));
 }
 
+template <int MS>
 __global__ void __launch_bounds__(HC_THREADS) hyper_step_kernel(HyperArgs g) {
   extern __shared__ float su[];                      // [W] the read's sum, then 32 floats for the block's reduction
   float* red = su + g.W;
-  __shared__ float smix[HC_MAX_STREAMS * HC_MAX_STREAMS], sout[HC_MAX_STREAMS], sin_[HC_MAX_STREAMS];
+  __shared__ float smix[MS * MS], sout[MS], sin_[MS];
   const int S = g.S;
   if (threadIdx.x < S * S && g.y) smix[threadIdx.x] = __ldg(g.mix + threadIdx.x);
   if (threadIdx.x < S) {
@@ -58,36 +59,36 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_step_kernel(HyperArgs g) {
   float* xo = g.xout ? g.xout + t * S * g.W : nullptr;
   float ss = 0.0f;
   for (int c = threadIdx.x; c < g.W; c += HC_THREADS) {
-    float x[HC_MAX_STREAMS];
+    float x[MS];
 #pragma unroll
-    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+    for (int s = 0; s < MS; ++s)
       if (s < S) x[s] = __ldcg(xi + (g.s_in == 1 ? 0 : (int64_t)s * g.W) + c);
     if (g.y) {
       const float y = hc_load(g.y, g.y_dtype, t * g.W + c);
-      float nx[HC_MAX_STREAMS];
+      float nx[MS];
 #pragma unroll
-      for (int to = 0; to < HC_MAX_STREAMS; ++to) {
+      for (int to = 0; to < MS; ++to) {
         if (to < S) {
           float a = 0.0f;
 #pragma unroll
-          for (int s = 0; s < HC_MAX_STREAMS; ++s)
+          for (int s = 0; s < MS; ++s)
             if (s < S) a = fmaf(smix[s * S + to], x[s], a);
           nx[to] = fmaf(sout[to], y, a);
         }
       }
 #pragma unroll
-      for (int s = 0; s < HC_MAX_STREAMS; ++s)
+      for (int s = 0; s < MS; ++s)
         if (s < S) x[s] = nx[s];
     }
     if (xo && (g.y || g.s_in != S)) {
 #pragma unroll
-      for (int s = 0; s < HC_MAX_STREAMS; ++s)
+      for (int s = 0; s < MS; ++s)
         if (s < S) xo[(int64_t)s * g.W + c] = x[s];
     }
     if (g.w_in) {
       float u = 0.0f;
 #pragma unroll
-      for (int s = 0; s < HC_MAX_STREAMS; ++s)
+      for (int s = 0; s < MS; ++s)
         if (s < S) u = fmaf(sin_[s], x[s], u);
       su[c] = u;
       ss = fmaf(u, u, ss);
@@ -106,11 +107,11 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_step_kernel(HyperArgs g) {
 }
 
 // The same with four columns a thread (16-byte accesses of the streams): W a multiple of 4, everything aligned.
-template <typename TY, typename TR>
+template <typename TY, typename TR, int MS>
 __global__ void __launch_bounds__(HC_THREADS) hyper_step_vec_kernel(HyperArgs g) {
   extern __shared__ float su[];
   float* red = su + g.W;
-  __shared__ float smix[HC_MAX_STREAMS * HC_MAX_STREAMS], sout[HC_MAX_STREAMS], sin_[HC_MAX_STREAMS];
+  __shared__ float smix[MS * MS], sout[MS], sin_[MS];
   const int S = g.S;
   if (threadIdx.x < S * S && g.y) smix[threadIdx.x] = __ldg(g.mix + threadIdx.x);
   if (threadIdx.x < S) {
@@ -127,9 +128,9 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_step_vec_kernel(HyperArgs g)
   const TY* yp = static_cast<const TY*>(g.y);
   float ss = 0.0f;
   for (int c = threadIdx.x * 4; c < g.W; c += HC_THREADS * 4) {
-    float x[HC_MAX_STREAMS][4];
+    float x[MS][4];
 #pragma unroll
-    for (int s = 0; s < HC_MAX_STREAMS; ++s)
+    for (int s = 0; s < MS; ++s)
       if (s < S) load_vec_cg(xi + (g.s_in == 1 ? 0 : (int64_t)s * g.W) + c, x[s]);
     if (g.y) {
       float y[4];
@@ -140,22 +141,22 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_step_vec_kernel(HyperArgs g)
         y[0] = __uint_as_float(rr.x << 16); y[1] = __uint_as_float(rr.x & 0xffff0000u);
         y[2] = __uint_as_float(rr.y << 16); y[3] = __uint_as_float(rr.y & 0xffff0000u);
       }
-      float nx[HC_MAX_STREAMS][4];
+      float nx[MS][4];
 #pragma unroll
-      for (int to = 0; to < HC_MAX_STREAMS; ++to) {
+      for (int to = 0; to < MS; ++to) {
         if (to < S) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) {
             float a = 0.0f;
 #pragma unroll
-            for (int s = 0; s < HC_MAX_STREAMS; ++s)
+            for (int s = 0; s < MS; ++s)
               if (s < S) a = fmaf(smix[s * S + to], x[s][e], a);
             nx[to][e] = fmaf(sout[to], y[e], a);
           }
         }
       }
 #pragma unroll
-      for (int s = 0; s < HC_MAX_STREAMS; ++s)
+      for (int s = 0; s < MS; ++s)
         if (s < S) {
 #pragma unroll
           for (int e = 0; e < 4; ++e) x[s][e] = nx[s][e];
@@ -163,7 +164,7 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_step_vec_kernel(HyperArgs g)
     }
     if (xo && (g.y || g.s_in != S)) {
 #pragma unroll
-      for (int s = 0; s < HC_MAX_STREAMS; ++s)
+      for (int s = 0; s < MS; ++s)
         if (s < S) store_vec(xo + (int64_t)s * g.W + c, x[s]);
     }
     if (g.w_in) {
@@ -172,7 +173,7 @@ __global__ void __launch_bounds__(HC_THREADS) hyper_step_vec_kernel(HyperArgs g)
       for (int e = 0; e < 4; ++e) {
         float a = 0.0f;
 #pragma unroll
-        for (int s = 0; s < HC_MAX_STREAMS; ++s)
+        for (int s = 0; s < MS; ++s)
           if (s < S) a = fmaf(sin_[s], x[s][e], a);
         u[e] = a;
         ss = fmaf(a, a, ss);
@@ -246,15 +247,22 @@ extern "C" int exl3_hyper_step(const float* xin, int s_in, float* xout, int S, c
     }                                                                                                          \
     launch_pdl(KERNEL, dim3(n), dim3(HC_THREADS), smem, stream, g);                                            \
   } while (0)
-  if (!vec) {
-    EXL3_HC(hyper_step_kernel);
-  } else {
-    const bool yf = y == nullptr || y_dtype == DT_F32, rf = r == nullptr || r_dtype == DT_F32;
-    if (yf && rf) EXL3_HC((hyper_step_vec_kernel<float, float>));
-    else if (yf) EXL3_HC((hyper_step_vec_kernel<float, __nv_bfloat16>));
-    else if (rf) EXL3_HC((hyper_step_vec_kernel<__nv_bfloat16, float>));
-    else EXL3_HC((hyper_step_vec_kernel<__nv_bfloat16, __nv_bfloat16>));
-  }
+#define EXL3_HC_MS(MS)                                                                                         \
+  do {                                                                                                         \
+    if (!vec) {                                                                                                \
+      EXL3_HC((hyper_step_kernel<MS>));                                                                        \
+    } else {                                                                                                   \
+      const bool yf = y == nullptr || y_dtype == DT_F32, rf = r == nullptr || r_dtype == DT_F32;               \
+      if (yf && rf) EXL3_HC((hyper_step_vec_kernel<float, float, MS>));                                        \
+      else if (yf) EXL3_HC((hyper_step_vec_kernel<float, __nv_bfloat16, MS>));                                 \
+      else if (rf) EXL3_HC((hyper_step_vec_kernel<__nv_bfloat16, float, MS>));                                 \
+      else EXL3_HC((hyper_step_vec_kernel<__nv_bfloat16, __nv_bfloat16, MS>));                                 \
+    }                                                                                                          \
+  } while (0)
+  if (S <= 4) EXL3_HC_MS(4);
+  else if (S <= 8) EXL3_HC_MS(8);
+  else EXL3_HC_MS(16);
+#undef EXL3_HC_MS
 #undef EXL3_HC
   return launch_status("hyper_step");
 }

@@ -33,7 +33,7 @@ def step_layout(rows):
 
 @pytest.mark.parametrize("y_dt", TYPES)
 @pytest.mark.parametrize("r_dt", TYPES)
-@pytest.mark.parametrize("S, W", [(1, 96), (2, 100), (3, 37), (5, 1032), (8, 64)])
+@pytest.mark.parametrize("S, W", [(1, 96), (2, 100), (3, 37), (5, 1032), (8, 64), (11, 40), (16, 24)])
 def test_hyper_step(S, W, y_dt, r_dt):
     g = torch.Generator().manual_seed(S * 1000 + W)
     k_ = K()
